@@ -4,7 +4,8 @@ from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from .llama import LlamaConfig, RopeScaling
 from .zemivik import ZemivikConfig
 from .dofipel import DofipelConfig
+from .ganupel import GanupelConfig
 
 __all__ = ["Architecture", "ConfigError", "architecture_of", "known_architectures", "load_config",
            "read_config_json", "register_architecture", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec",
-           "LlamaConfig", "RopeScaling", "ZemivikConfig", "DofipelConfig"]
+           "LlamaConfig", "RopeScaling", "ZemivikConfig", "DofipelConfig", "GanupelConfig"]

@@ -21,6 +21,8 @@
 // query head and distance (query position minus key position, distances of bias_len - 1 and more share the last entry) is
 // added to the score after the cap, unscaled. `v_ld`: elements between the starts of two value rows of a page, for values
 // that are a column range of wider rows (a latent that serves as key and value at once: v_cache then points into k_cache).
+// `sig_bias` [n_q]: no softmax at all; a visible key's weight is sigmoid(score + sig_bias[head]) and the weights are not
+// normalised over the keys (out_i = sum_j sigmoid(s_ij + b) v_j); excludes the sink.
 #include "common.cuh"
 #include <math.h>
 
@@ -37,7 +39,8 @@ attention_paged_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                        const int* __restrict__ seq_slot, const int* __restrict__ block_table, int max_pages,
                        int page_size, int n_items, int n_q, int n_kv, int hd, int hdv, float scale, int window,
                        int keep_first, int sink, const T* __restrict__ gate, int gate_ld, int v_ld, float softcap,
-                       const float* __restrict__ dist_bias, int bias_len, const float* __restrict__ sink_vals) {
+                       const float* __restrict__ dist_bias, int bias_len, const float* __restrict__ sink_vals,
+                       const float* __restrict__ sig_bias) {
   extern __shared__ float q_smem[];  // [kAttnWarps][hd]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * kAttnWarps + warp;
@@ -62,6 +65,7 @@ attention_paged_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
   float m = -INFINITY, l = 0.f;
   const float* bias_row = dist_bias ? dist_bias + (size_t)h * bias_len : nullptr;
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const float sig_b = sig_bias ? sig_bias[h] : 0.f;
 
   for (int seg = 0; seg < 2; ++seg) {
     const int first = seg == 0 ? 0 : lo;
@@ -90,13 +94,18 @@ attention_paged_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
         if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
         if (bias_row) s += bias_row[min(pos - j, bias_len - 1)];
       }
-      const float m_new = fmaxf(m, warp_max(s));
-      const float p = valid ? expf(s - m_new) : 0.f;
-      const float alpha = expf(m - m_new);  // m == -inf on the first chunk gives 0
-      l = l * alpha + warp_sum(p);
+      float p;
+      if (sig_bias) {
+        p = valid ? 1.f / (1.f + expf(-(s + sig_b))) : 0.f;
+      } else {
+        const float m_new = fmaxf(m, warp_max(s));
+        p = valid ? expf(s - m_new) : 0.f;
+        const float alpha = expf(m - m_new);  // m == -inf on the first chunk gives 0
+        l = l * alpha + warp_sum(p);
 #pragma unroll
-      for (int i = 0; i < kAcc; ++i) acc[i] *= alpha;
-      m = m_new;
+        for (int i = 0; i < kAcc; ++i) acc[i] *= alpha;
+        m = m_new;
+      }
       const int n_here = min(32, last - base + 1);
       for (int jj = 0; jj < n_here; ++jj) {
         const float pj = __shfl_sync(0xffffffffu, p, jj);
@@ -120,7 +129,7 @@ attention_paged_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
 #pragma unroll
     for (int i = 0; i < kAcc; ++i) acc[i] *= alpha;
   }
-  const float inv_l = 1.f / l;
+  const float inv_l = sig_bias ? 1.f : 1.f / l;
   T* orow = out + ((size_t)t * n_q + h) * hdv;
   const T* grow = gate ? gate + (size_t)t * gate_ld + (size_t)h * hdv : nullptr;
 #pragma unroll
@@ -144,29 +153,32 @@ static void attention_paged_launch(bool vec, int blocks, size_t smem, cudaStream
                                    const int* tok_seq, const int* seq_slot, const int* block_table, int max_pages,
                                    int page_size, int n_items, int n_q, int n_kv, int hd, int hdv, float scale,
                                    int window, int keep_first, int sink, const void* gate, int gate_ld, int v_ld,
-                                   float softcap, const float* dist_bias, int bias_len, const float* sink_vals) {
+                                   float softcap, const float* dist_bias, int bias_len, const float* sink_vals,
+                                   const float* sig_bias) {
   if (vec)
     attention_paged_kernel<T, true, MAXHD><<<blocks, kAttnWarps * 32, smem, stream>>>(
         (const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, tok_pos, tok_seq, seq_slot, block_table, max_pages,
         page_size, n_items, n_q, n_kv, hd, hdv, scale, window, keep_first, sink, (const T*)gate, gate_ld, v_ld, softcap,
-        dist_bias, bias_len, sink_vals);
+        dist_bias, bias_len, sink_vals, sig_bias);
   else
     attention_paged_kernel<T, false, MAXHD><<<blocks, kAttnWarps * 32, smem, stream>>>(
         (const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, tok_pos, tok_seq, seq_slot, block_table, max_pages,
         page_size, n_items, n_q, n_kv, hd, hdv, scale, window, keep_first, sink, (const T*)gate, gate_ld, v_ld, softcap,
-        dist_bias, bias_len, sink_vals);
+        dist_bias, bias_len, sink_vals, sig_bias);
 }
 
 // q [n_tokens, n_q * hd]; out [n_tokens, n_q * hdv]; k_cache [n_pages, n_kv, page_size, hd]; v_cache rows of hdv
 // elements, v_ld apart (v_ld == hdv: a tensor [n_pages, n_kv, page_size, hdv] of its own); gate (or null) rows of
 // n_q * hdv elements, gate_ld apart; all of `dtype`. dist_bias float32 [n_q, bias_len] or null; sink_vals float32 [n_q]
-// or null (with sink != 0: the sink's score is 0). Any hd, hdv up to 1024.
-extern "C" int llmie_attention_paged_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
+// or null (with sink != 0: the sink's score is 0); sig_bias float32 [n_q] or null. Any hd, hdv up to 1024.
+extern "C" int llmie_attention_paged_sig(const void* q, const void* k_cache, const void* v_cache, void* out,
                                         const int* tok_pos, const int* tok_seq, const int* seq_slot,
                                         const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
                                         int n_kv, int hd, int hdv, float scale, int window, int keep_first, int sink,
                                         const void* gate, int gate_ld, int v_ld, float softcap, const float* dist_bias,
-                                        int bias_len, const float* sink_vals, int dtype, cudaStream_t stream) {
+                                        int bias_len, const float* sink_vals, const float* sig_bias, int dtype,
+                                        cudaStream_t stream) {
+  if (sig_bias && sink) return LLMIE_ERR_BAD_ARG;
   if (n_tokens < 0 || n_q <= 0 || n_kv <= 0 || hd <= 0 || hdv <= 0 || page_size <= 0 || max_pages <= 0)
     return LLMIE_ERR_BAD_ARG;
   if (n_q % n_kv || keep_first < 0 || window < 0 || (gate && gate_ld < n_q * hdv)) return LLMIE_ERR_BAD_ARG;
@@ -184,7 +196,7 @@ extern "C" int llmie_attention_paged_ex(const void* q, const void* k_cache, cons
 #define LLMIE_ATTN_ARGS                                                                                              \
   vec, blocks, smem, stream, q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, \
       (int)n_items, n_q, n_kv, hd, hdv, scale, window, keep_first, sink, gate, gate_ld, v_ld, softcap, dist_bias,    \
-      bias_len, sink_vals
+      bias_len, sink_vals, sig_bias
   if (dtype == LLMIE_F32) {
     if (wide) attention_paged_launch<float, kWideHeadDim>(LLMIE_ATTN_ARGS);
     else attention_paged_launch<float, kMaxHeadDim>(LLMIE_ATTN_ARGS);
@@ -195,4 +207,15 @@ extern "C" int llmie_attention_paged_ex(const void* q, const void* k_cache, cons
 #undef LLMIE_ATTN_ARGS
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
+}
+
+extern "C" int llmie_attention_paged_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                        const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
+                                        int n_kv, int hd, int hdv, float scale, int window, int keep_first, int sink,
+                                        const void* gate, int gate_ld, int v_ld, float softcap, const float* dist_bias,
+                                        int bias_len, const float* sink_vals, int dtype, cudaStream_t stream) {
+  return llmie_attention_paged_sig(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_table, max_pages,
+                                   page_size, n_tokens, n_q, n_kv, hd, hdv, scale, window, keep_first, sink, gate,
+                                   gate_ld, v_ld, softcap, dist_bias, bias_len, sink_vals, nullptr, dtype, stream);
 }

@@ -171,13 +171,13 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const float2* __restrict__ table, const int* __restrict__ tok_pos,
                                   const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                                   const int* __restrict__ block_table, int max_pages, int page_size,
-                                  int n_q, int n_kv, int hd, int rot_dim, int table_len, int write_kv) {
+                                  int n_q, int n_kv, int hd, int hdv, int rot_dim, int table_len, int write_kv) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   int pos = tok_pos[t];
   const int half = rot_dim >> 1;
-  const int row_w = (n_q + 2 * n_kv) * hd;
+  const int row_w = (n_q + n_kv) * hd + n_kv * hdv;
   const T* src = qkv + (size_t)t * row_w;
   const int tpos = pos < table_len ? pos : table_len - 1;  // the host refuses pos >= table_len
   const float2* cs = table ? table + (size_t)tpos * half : nullptr;
@@ -211,7 +211,6 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     const int i = it % hd;
     const int hk = it / hd;
     const size_t dst = (((size_t)page * n_kv + hk) * page_size + in_page) * hd;
-    v_cache[dst + i] = vs[it];
     if (cs && i < rot_dim) {
       if (i < half) {
         const float x1 = to_f32(ks[it]), x2 = to_f32(ks[it + half]);
@@ -222,6 +221,12 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     } else {
       k_cache[dst + i] = ks[it];
     }
+  }
+  const int v_items = n_kv * hdv;
+  for (int it = threadIdx.x; it < v_items; it += blockDim.x) {
+    const int i = it % hdv;
+    const int hk = it / hdv;
+    v_cache[(((size_t)page * n_kv + hk) * page_size + in_page) * hdv + i] = vs[it];
   }
 }
 
@@ -417,19 +422,21 @@ extern "C" int llmie_swiglu(const void* gate_up, void* out, int n_tokens, int ff
   return LLMIE_OK;
 }
 
-extern "C" int llmie_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const float* table,
-                                const int* tok_pos, const int* tok_seq, const int* seq_slot,
-                                const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
-                                int n_kv, int hd, int rot_dim, int table_len, int write_kv, int dtype,
-                                cudaStream_t stream) {
-  if (n_tokens < 0 || n_q <= 0 || n_kv < 0 || hd <= 0 || page_size <= 0 || max_pages <= 0) return LLMIE_ERR_BAD_ARG;
+// hdv: the size of a value head (the packed row is [n_q hd | n_kv hd | n_kv hdv], the value cache's rows hold hdv)
+extern "C" int llmie_rope_store_ex(const void* qkv, void* q_out, void* k_cache, void* v_cache, const float* table,
+                                   const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                   const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
+                                   int n_kv, int hd, int hdv, int rot_dim, int table_len, int write_kv, int dtype,
+                                   cudaStream_t stream) {
+  if (n_tokens < 0 || n_q <= 0 || n_kv < 0 || hd <= 0 || hdv <= 0 || page_size <= 0 || max_pages <= 0)
+    return LLMIE_ERR_BAD_ARG;
   if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1)) return LLMIE_ERR_BAD_ARG;
   if (table && table_len <= 0) return LLMIE_ERR_BAD_ARG;
   if (n_tokens == 0) return LLMIE_OK;
   int threads = ((n_q * hd / 2 + 31) / 32) * 32;
   threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
   const float2* tab = reinterpret_cast<const float2*>(table);
-  if (dtype == LLMIE_BF16 && table && rot_dim == hd && hd % 16 == 0 && aligned16(qkv) && aligned16(q_out) &&
+  if (dtype == LLMIE_BF16 && table && rot_dim == hd && hdv == hd && hd % 16 == 0 && aligned16(qkv) && aligned16(q_out) &&
       (!write_kv || (aligned16(k_cache) && aligned16(v_cache)))) {
     int vt = (((n_q + n_kv) * (hd / 16) + 31) / 32) * 32;
     vt = vt < 32 ? 32 : (vt > 256 ? 256 : vt);
@@ -442,15 +449,24 @@ extern "C" int llmie_rope_store(const void* qkv, void* q_out, void* k_cache, voi
   if (dtype == LLMIE_F32)
     launch_k(rope_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, 
         (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, tab, tok_pos, tok_seq, seq_slot,
-        block_table, max_pages, page_size, n_q, n_kv, hd, rot_dim, table_len, write_kv);
+        block_table, max_pages, page_size, n_q, n_kv, hd, hdv, rot_dim, table_len, write_kv);
   else if (dtype == LLMIE_BF16)
     launch_k(rope_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tab,
-        tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, rot_dim, table_len, write_kv);
+        tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, hdv, rot_dim, table_len, write_kv);
   else
     return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
+}
+
+extern "C" int llmie_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const float* table,
+                                const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
+                                int n_kv, int hd, int rot_dim, int table_len, int write_kv, int dtype,
+                                cudaStream_t stream) {
+  return llmie_rope_store_ex(qkv, q_out, k_cache, v_cache, table, tok_pos, tok_seq, seq_slot, block_table, max_pages,
+                             page_size, n_tokens, n_q, n_kv, hd, hd, rot_dim, table_len, write_kv, dtype, stream);
 }
 
 extern "C" int llmie_prepare_decode(const int* slots, const int* seq_lens, int* tok_pos, int* tok_seq, int* cu_q,

@@ -113,6 +113,8 @@ grouped_gemm_kernel(const GroupedArgs p) {
         // the gate is rounded to the activation type before the activation, as a separate product would leave it
         const float g = to_f32(from_f32<TC>(v)), u = to_f32(from_f32<TC>(acc[DUAL ? 1 : 0][i][j]));
         v = apply_act(g, p.act) * u;
+      } else if (p.act) {
+        v = apply_act(to_f32(from_f32<TC>(v)), p.act);      // a single product with its activation
       }
       C[(size_t)rc * p.ldc + gn] = from_f32<TC>(v);
     }
@@ -256,6 +258,8 @@ grouped_gemm_mma_kernel(const GroupedArgs p, const int vec) {
         if (DUAL) {
           const float gt = to_f32(from_f32<TC>(v)), up = to_f32(from_f32<TC>(acc[NW - 1][i][2 * half + e]));
           v = apply_act(gt, p.act) * up;
+        } else if (p.act) {
+          v = apply_act(to_f32(from_f32<TC>(v)), p.act);
         }
         C[(size_t)rc * p.ldc + gn] = from_f32<TC>(v);
       }
@@ -295,7 +299,8 @@ extern "C" int llmie_grouped_gemm_tile_rows(int small) { return small ? 16 : 64;
 
 // A, W of in_dtype; C of out_dtype. `groups` > 0 with tile_group == null: the batched form over M rows. tile_group !=
 // null: the routed form over `n_tiles` tiles of sorted positions (M = number of positions, padding included).
-// `small` picks tiles of 16 rows (few rows per group) instead of 64. dual: W holds [gate | up], act is applied.
+// `small` picks tiles of 16 rows (few rows per group) instead of 64. dual: W holds [gate | up], act is applied to the
+// gate; without dual a non-zero act is applied to the product itself.
 extern "C" int llmie_grouped_gemm_nt(const void* A, long long lda, long long a_gcs, const int* a_rows, const void* W,
                                      long long w_gs, long long ldw, void* C, long long ldc, long long c_gcs,
                                      const int* c_rows, const int* tile_group, int n_tiles, int groups, int M, int N,

@@ -4,9 +4,12 @@
 //   route     z = W_r x + b in float32 (a block per token, each lane a fixed share of the columns, so a token's logits do
 //             not depend on the batch); the `top` largest logits are chosen (ties: the lower index), their weights are
 //             the softmax over the chosen logits alone
+//             second rule (`mode` 1): scores = softmax over ALL logits; the `top` largest of score + correction are chosen
+//             (the correction steers the choice only); weights = the chosen scores / (their sum + 1e-20) * a constant
 //   sort      the (token, choice) pairs grouped by expert into tiles of `tile` positions, padded per expert; one block,
 //             no host involvement, so the step can be captured: sizes are upper bounds, unused tiles say -1
-//   combine   out[t] = sum_k weight[t, k] * y[t * top + k] (+ shared[t]) in float32, in the order of k
+//   combine   out[t] = sum_k weight[t, k] * y[t * top + k] (+ shared[t]) in float32, in the order of k; a choice whose
+//             id is not below the number of real experts stands for an expert that returns its input: weight * x[t]
 #include "common.cuh"
 #include <math.h>
 
@@ -17,12 +20,14 @@ constexpr int kRouteWarps = 8;
 template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
-                 int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int d, int n_experts, int top) {
+                 int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int d, int n_experts, int top,
+                 int mode, const float* __restrict__ correction, float out_scale) {
   // A block per token: the token's row is staged once as float32, its warps share out the experts, and a warp's lanes
   // take fixed columns of a dot product (four running sums each, added in a fixed order).
-  extern __shared__ __align__(16) float route_smem[];            // [d] the row | [n_experts] the logits
+  extern __shared__ __align__(16) float route_smem[];            // [d] the row | [n_experts] the logits | scores
   float* xs = route_smem;
   float* z = route_smem + d;
+  float* sc = z + n_experts;                                     // mode 1: the scores the weights are made of
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -63,6 +68,22 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
   __syncthreads();
   if (warp != 0) return;
   __syncwarp();
+  if (mode == 1) {
+    // scores over all experts; z becomes what the choice is made by
+    float mx = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < n_experts; e += 32) { const float p = expf(z[e] - mx); sc[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    const float inv_sum = 1.f / sum;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float p = sc[e] * inv_sum;
+      sc[e] = p;
+      z[e] = p + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+  }
   float first = 0.f, denom = 0.f, mine = 0.f;      // lane k keeps the k-th chosen logit
   int mine_id = 0;
   for (int k = 0; k < top; ++k) {
@@ -79,7 +100,7 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
       if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
     }
     if (k == 0) first = best;
-    const float p = expf(best - first);
+    const float p = mode == 1 ? (best_e < n_experts ? sc[best_e] : 0.f) : expf(best - first);
     denom += p;
     if ((k & 31) == lane) { mine = p; mine_id = best_e; }
     if (lane == 0 && best_e < n_experts) z[best_e] = -INFINITY;
@@ -94,7 +115,7 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
     }
   }
   __syncwarp();
-  const float inv = 1.f / denom;
+  const float inv = mode == 1 ? out_scale / (denom + 1e-20f) : 1.f / denom;
   for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= inv;
 }
 
@@ -180,25 +201,64 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
   }
 }
 
+__device__ __forceinline__ float load_any(const void* p, int dtype, size_t i) {
+  return dtype == LLMIE_F32 ? reinterpret_cast<const float*>(p)[i] : to_f32(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// The combine with experts that return their input: a choice whose id is n_real or more adds weight * x[t].
+__global__ void moe_combine_identity_kernel(const void* __restrict__ y, int y_dtype, const int* __restrict__ pair_pos,
+                                            const float* __restrict__ weights, const int* __restrict__ ids, int n_real,
+                                            const void* __restrict__ x, int x_dtype, float* __restrict__ out, int d,
+                                            int top, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / d;
+    const int c = (int)(i - t * d);
+    float s = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const float w = weights[t * top + k];
+      if (ids[t * top + k] >= n_real) {
+        s = fmaf(w, load_any(x, x_dtype, i), s);
+      } else {
+        const size_t row = pair_pos ? (size_t)pair_pos[t * top + k] : t * top + k;
+        s = fmaf(w, load_any(y, y_dtype, row * d + c), s);
+      }
+    }
+    out[i] = s;
+  }
+}
+
 }  // namespace llmie
 
 using namespace llmie;
 
 // x [T, d] of x_dtype; w float32 [E, d]; bias float32 [E] or null; ids int32 [T, top]; weights float32 [T, top].
-extern "C" int llmie_moe_route(const void* x, int x_dtype, const float* w, const float* bias, int* ids, float* weights,
-                               int n_tokens, int d, int n_experts, int top, cudaStream_t stream) {
+// mode 0: the rule above (bias added to the logits, softmax over the chosen logits). mode 1: softmax over all logits,
+// choice by score + correction (float32 [E] or null), weights = chosen scores / (their sum + 1e-20) * out_scale.
+extern "C" int llmie_moe_route_ex(const void* x, int x_dtype, const float* w, const float* bias, int* ids,
+                                  float* weights, int n_tokens, int d, int n_experts, int top, int mode,
+                                  const float* correction, float out_scale, cudaStream_t stream) {
   if (n_tokens < 0 || d <= 0 || n_experts <= 0 || top <= 0 || top > n_experts) return LLMIE_ERR_BAD_ARG;
+  if (mode != 0 && mode != 1) return LLMIE_ERR_BAD_ARG;
   if (x_dtype != LLMIE_F32 && x_dtype != LLMIE_BF16) return LLMIE_ERR_DTYPE;
-  const size_t smem = ((size_t)d + n_experts) * sizeof(float);
+  const size_t smem = ((size_t)d + 2 * (size_t)n_experts) * sizeof(float);
   if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (n_tokens == 0) return LLMIE_OK;
   const int blocks = n_tokens;
   if (x_dtype == LLMIE_F32)
-    launch_k(moe_route_kernel<float>, dim3(blocks), dim3(kRouteWarps * 32), smem, stream, (const float*)x, w, bias, ids, weights, n_tokens, d, n_experts, top);
+    launch_k(moe_route_kernel<float>, dim3(blocks), dim3(kRouteWarps * 32), smem, stream, (const float*)x, w, bias, ids, weights, n_tokens, d, n_experts, top, mode, correction, out_scale);
   else
-    launch_k(moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(kRouteWarps * 32), smem, stream, (const __nv_bfloat16*)x, w, bias, ids, weights, n_tokens, d, n_experts, top);
+    launch_k(moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(kRouteWarps * 32), smem, stream, (const __nv_bfloat16*)x, w, bias, ids, weights, n_tokens, d, n_experts, top, mode, correction, out_scale);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
+}
+
+extern "C" int llmie_moe_route(const void* x, int x_dtype, const float* w, const float* bias, int* ids, float* weights,
+                               int n_tokens, int d, int n_experts, int top, cudaStream_t stream) {
+  return llmie_moe_route_ex(x, x_dtype, w, bias, ids, weights, n_tokens, d, n_experts, top, 0, nullptr, 1.f, stream);
 }
 
 // ids int32 [n_pairs] (pair = token * top + choice); sorted_token, sorted_pair int32 [max_tiles * tile];
@@ -237,6 +297,24 @@ extern "C" int llmie_moe_combine(const void* y, int y_dtype, const int* pair_pos
     if (sb) launch_k(moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)y, pair_pos, weights, (const __nv_bfloat16*)shared_out, out, d, top, total);
     else launch_k(moe_combine_kernel<float, __nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)y, pair_pos, weights, (const float*)shared_out, out, d, top, total);
   }
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// The same with experts that return their input: ids int32 [T, top]; a choice with an id of n_real or more adds
+// weight * x[t] (x [T, d] of x_dtype) and has no row in y.
+extern "C" int llmie_moe_combine_identity(const void* y, int y_dtype, const int* pair_pos, const float* weights,
+                                          const int* ids, int n_real, const void* x, int x_dtype, float* out,
+                                          int n_tokens, int d, int top, cudaStream_t stream) {
+  if (n_tokens < 0 || d <= 0 || top <= 0 || !ids || !x || n_real < 0) return LLMIE_ERR_BAD_ARG;
+  if ((y_dtype != LLMIE_F32 && y_dtype != LLMIE_BF16) || (x_dtype != LLMIE_F32 && x_dtype != LLMIE_BF16))
+    return LLMIE_ERR_DTYPE;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t total = (size_t)n_tokens * d;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  launch_k(moe_combine_identity_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, y, y_dtype, pair_pos, weights, ids,
+           n_real, x, x_dtype, out, d, top, total);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }

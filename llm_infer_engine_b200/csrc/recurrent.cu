@@ -1,0 +1,375 @@
+// Mixers that carry a fixed-size state from token to token instead of reading a cache of keys: a gated linear
+// recurrence over a matrix state per head, and a gated linear recurrent unit over a vector state behind a short causal
+// convolution. Everything that enters a recurrence (gates, decays, the state, the norms of what is read) is float32 in
+// both precisions; the projections that feed the kernels have the activation type.
+//
+// Packed tokens: sequence s of the step owns rows cu_q[s] .. cu_q[s+1]-1, its state lives in row seq_slot[s] of a
+// [slots, ...] float32 tensor and is read at the start and written at the end, so a sequence fed in pieces, or token
+// by token, goes through exactly the same arithmetic as one fed whole.
+//
+//   matrix_gates       q = silu(q_raw), f = l + (1 - l) sigmoid(f_raw + b)           element-wise, float32 out
+//   matrix_scan        S <- diag(f_t) S + (1 - f_t) v_t^T ; o_t = S^T q_t            S [dim, vdim] per head
+//   head_rmsnorm       o / sqrt(mean(o^2) + eps) * w over each head's vdim
+//   causal_conv        u_t = b + sum_j taps[:, K-1-j] x_(t-j), x before the step from the state's last K-1 inputs
+//   unit_gate_values   a = exp(-c r softplus(lam)), drive = sqrt(1 - a^2) i u, r and i sigmoids of given pre-activations
+//   unit_scan          S <- a_t S + drive_t ; out_t = S act(y_raw + b) ; the new conv state
+#include "common.cuh"
+#include <math.h>
+
+namespace llmie {
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// ------------------------------------------------------------------------------------------ matrix state
+template <typename T>
+__global__ void matrix_gates_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off,
+                                    const float* __restrict__ f_bias, const float* __restrict__ lower,
+                                    float* __restrict__ q_out, float* __restrict__ f_out, int n, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / n;
+    const int c = (int)(i - t * n);
+    const T* row = proj + t * ld;
+    const float q = to_f32(row[q_off + c]);
+    const float z = to_f32(row[f_off + c]) + f_bias[c];
+    const float l = lower[c];
+    q_out[i] = q * sigmoidf_(q);
+    f_out[i] = l + (1.f - l) * sigmoidf_(z);
+  }
+}
+
+constexpr int kScanThreads = 128;
+constexpr int kScanR = 16;          // state rows a thread keeps at most
+
+// grid (column tiles, heads, sequences). A thread owns column j of its head's state and the rows [s R, (s+1) R) of it,
+// S = slices (a power of two up to 32, lanes that differ in their low bits), R = ceil(dim / S) <= kScanR. The next
+// token's gate, query and value are requested before the current token's products.
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, const T* __restrict__ v, int v_ld,
+                   float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
+                   float* __restrict__ o, int H, int D, int Dv, int S, int R, int write_state) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = threadIdx.x & (S - 1);
+  const int col = threadIdx.x / S;
+  const int j = blockIdx.x * (kScanThreads / S) + col;
+  const int h = blockIdx.y, seq = blockIdx.z;
+  const bool live = j < Dv;
+  const int jj = live ? j : Dv - 1;
+  const int i0 = s * R;
+  const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+  const int slot = seq_slot[seq];
+  float* st = state + (((size_t)slot * H + h) * D) * Dv + jj;
+  float St[kScanR];
+#pragma unroll
+  for (int r = 0; r < kScanR; ++r) St[r] = (r < R && i0 + r < D) ? st[(size_t)(i0 + r) * Dv] : 0.f;
+  float f[kScanR], q[kScanR], vj = 0.f;
+  const size_t HD = (size_t)H * D;
+  auto fetch = [&](int t) {
+    const float* fr = fg + (size_t)t * HD + (size_t)h * D + i0;
+    const float* qr = qa + (size_t)t * HD + (size_t)h * D + i0;
+#pragma unroll
+    for (int r = 0; r < kScanR; ++r) {
+      const bool ok = r < R && i0 + r < D;
+      f[r] = ok ? fr[r] : 0.f;
+      q[r] = ok ? qr[r] : 0.f;
+    }
+    vj = to_f32(v[(size_t)t * v_ld + (size_t)h * Dv + jj]);
+  };
+  if (t0 < t1) fetch(t0);
+  for (int t = t0; t < t1; ++t) {
+    float cf[kScanR], cq[kScanR];
+    const float cv = vj;
+#pragma unroll
+    for (int r = 0; r < kScanR; ++r) { cf[r] = f[r]; cq[r] = q[r]; }
+    if (t + 1 < t1) fetch(t + 1);
+    float acc = 0.f;
+#pragma unroll
+    for (int r = 0; r < kScanR; ++r) {
+      St[r] = fmaf(cf[r], St[r], (1.f - cf[r]) * cv);
+      acc = fmaf(St[r], cq[r], acc);
+    }
+    for (int off = 1; off < S; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (s == 0 && live) o[(size_t)t * H * Dv + (size_t)h * Dv + j] = acc;
+  }
+  if (write_state && live) {
+#pragma unroll
+    for (int r = 0; r < kScanR; ++r)
+      if (r < R && i0 + r < D) st[(size_t)(i0 + r) * Dv] = St[r];
+  }
+}
+
+// a warp per (token, head): o float32 [T, H * Dv] -> y of the activation type
+template <typename T>
+__global__ void head_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
+                                    T* __restrict__ y, int Dv, size_t n_items) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t item = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= n_items) return;
+  const float* row = o + item * Dv;
+  float ss = 0.f;
+  for (int i = lane; i < Dv; i += 32) { const float x = row[i]; ss = fmaf(x, x, ss); }
+  ss = warp_sum(ss);
+  const float r = 1.f / sqrtf(ss / (float)Dv + eps);
+  for (int i = lane; i < Dv; i += 32) y[item * Dv + i] = from_f32<T>(row[i] * r * w[i]);
+}
+
+// ------------------------------------------------------------------------------------------ vector state
+constexpr int kMaxTaps = 16;
+
+// a thread per (token, channel). x = proj[:, x_off + c] + x_bias; inputs before the step come from conv_state
+// [slots, K-1, C] (the last K-1 inputs of the sequence so far, zeros at its start).
+template <typename T>
+__global__ void causal_conv_kernel(const T* __restrict__ proj, int ld, int x_off, const float* __restrict__ x_bias,
+                                   const float* __restrict__ taps, const float* __restrict__ conv_bias,
+                                   const float* __restrict__ conv_state, const int* __restrict__ cu_q,
+                                   const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                                   float* __restrict__ u, int C, int K, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const int t = (int)(i / C);
+    const int c = (int)(i - (size_t)t * C);
+    const int seq = tok_seq[t];
+    const int p = t - cu_q[seq];                      // place within this step's piece of the sequence
+    const float* old = conv_state + (size_t)seq_slot[seq] * (K - 1) * C + c;
+    const float xb = x_bias ? x_bias[c] : 0.f;
+    float acc = conv_bias ? conv_bias[c] : 0.f;
+    for (int j = K - 1; j >= 0; --j) {                // oldest input first: a fixed order of summation
+      const int m = p - j;
+      const float x = m >= 0 ? to_f32(proj[(size_t)(t - j) * ld + x_off + c]) + xb : old[(size_t)(K - 1 + m) * C];
+      acc = fmaf(taps[(size_t)c * K + (K - 1 - j)], x, acc);
+    }
+    u[i] = acc;
+  }
+}
+
+// gates [T, groups * 2 * bw]: per group the pre-activations of r (bw) and then of i (bw). In place: r's place receives
+// a = exp(-c r softplus(lam)), i's place the drive sqrt(1 - a^2) * i * u.
+__global__ void unit_gate_values_kernel(float* __restrict__ gates, const float* __restrict__ u,
+                                        const float* __restrict__ r_bias, const float* __restrict__ i_bias,
+                                        const float* __restrict__ lam, float c_decay, int C, int bw, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / C;
+    const int c = (int)(i - t * C);
+    const int g = c / bw, e = c - g * bw;
+    float* gr = gates + t * 2 * C + (size_t)g * 2 * bw + e;
+    const float r = sigmoidf_(gr[0] + r_bias[c]);
+    const float in = sigmoidf_(gr[bw] + i_bias[c]);
+    const float log_a = -c_decay * r * softplusf_(lam[c]);
+    const float a = expf(log_a);
+    gr[0] = a;
+    gr[bw] = sqrtf(-expm1f(2.f * log_a)) * (in * u[i]);     // 1 - a^2 without cancellation near a = 1
+  }
+}
+
+// a thread per (sequence, channel): the recurrence over the step's tokens, the output gate act(y_raw + y_bias), and
+// the new state of the recurrence and of the convolution.
+template <typename T>
+__global__ void unit_scan_kernel(const float* __restrict__ gates, const T* __restrict__ proj, int ld, int y_off,
+                                 int x_off, const float* __restrict__ y_bias, const float* __restrict__ x_bias,
+                                 int act, float* __restrict__ state, float* __restrict__ conv_state,
+                                 const int* __restrict__ cu_q, const int* __restrict__ seq_slot, T* __restrict__ out,
+                                 int C, int bw, int K, int write_state) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int seq = blockIdx.y;
+  if (c >= C) return;
+  const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+  const int slot = seq_slot[seq];
+  const int g = c / bw, e = c - g * bw;
+  const float yb = y_bias ? y_bias[c] : 0.f;
+  float S = state[(size_t)slot * C + c];
+  const float* gr = gates + (size_t)g * 2 * bw + e;
+  constexpr int U = 4;
+  int t = t0;
+  for (; t + U <= t1; t += U) {
+    float a[U], d[U], y[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      a[k] = gr[(size_t)(t + k) * 2 * C];
+      d[k] = gr[(size_t)(t + k) * 2 * C + bw];
+      y[k] = apply_act(to_f32(proj[(size_t)(t + k) * ld + y_off + c]) + yb, act);
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      S = fmaf(a[k], S, d[k]);
+      out[(size_t)(t + k) * C + c] = from_f32<T>(S * y[k]);
+    }
+  }
+  for (; t < t1; ++t) {
+    S = fmaf(gr[(size_t)t * 2 * C], S, gr[(size_t)t * 2 * C + bw]);
+    out[(size_t)t * C + c] = from_f32<T>(S * apply_act(to_f32(proj[(size_t)t * ld + y_off + c]) + yb, act));
+  }
+  if (!write_state) return;
+  state[(size_t)slot * C + c] = S;
+  // the last K-1 inputs of the sequence: this step's, and before them what the state held
+  float* cs = conv_state + (size_t)slot * (K - 1) * C + c;
+  const int n = t1 - t0;
+  const float xb = x_bias ? x_bias[c] : 0.f;
+  float keep[kMaxTaps];
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) {
+    if (k < K - 1) {
+      const int m = n - (K - 1) + k;                  // place within the step, negative = before it
+      keep[k] = m >= 0 ? to_f32(proj[(size_t)(t0 + m) * ld + x_off + c]) + xb : cs[(size_t)(K - 1 + m) * C];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k)
+    if (k < K - 1) cs[(size_t)k * C] = keep[k];
+}
+
+}  // namespace llmie
+
+using namespace llmie;
+
+static inline unsigned sweep_blocks(size_t total, int threads) {
+  size_t b = (total + threads - 1) / threads;
+  return (unsigned)(b > 148 * 16 ? 148 * 16 : (b ? b : 1));
+}
+
+// proj [T, ld] of `dtype` holds the raw query projection at column q_off and the raw gate projection at f_off, n
+// columns each; f_bias, lower float32 [n]; q_out, f_out float32 [T, n].
+extern "C" int llmie_matrix_gates(const void* proj, int ld, int q_off, int f_off, const float* f_bias, const float* lower,
+                                  float* q_out, float* f_out, int n_tokens, int n, int dtype, cudaStream_t stream) {
+  if (n_tokens < 0 || n <= 0 || q_off < 0 || f_off < 0 || ld < q_off + n || ld < f_off + n) return LLMIE_ERR_BAD_ARG;
+  if (!f_bias || !lower) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t total = (size_t)n_tokens * n;
+  const dim3 grid(sweep_blocks(total, 256)), block(256);
+  if (dtype == LLMIE_F32)
+    launch_k(matrix_gates_kernel<float>, grid, block, 0, stream, (const float*)proj, ld, q_off, f_off, f_bias, lower,
+             q_out, f_out, n, total);
+  else if (dtype == LLMIE_BF16)
+    launch_k(matrix_gates_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)proj, ld, q_off, f_off,
+             f_bias, lower, q_out, f_out, n, total);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// qa, fg float32 [T, H * D]; v rows of H * Dv elements of `dtype`, v_ld apart; state float32 [slots, H, D, Dv];
+// o float32 [T, H * Dv]. D up to 512.
+extern "C" int llmie_matrix_scan(const float* qa, const float* fg, const void* v, int v_ld, float* state,
+                                 const int* cu_q, const int* seq_slot, float* o, int n_seqs, int H, int D, int Dv,
+                                 int write_state, int dtype, cudaStream_t stream) {
+  if (n_seqs < 0 || H <= 0 || D <= 0 || Dv <= 0 || v_ld < H * Dv) return LLMIE_ERR_BAD_ARG;
+  if (D > 32 * kScanR) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (n_seqs == 0) return LLMIE_OK;
+  int S = 1;
+  while (S * kScanR < D) S <<= 1;
+  const int R = (D + S - 1) / S;
+  const int cols = kScanThreads / S;
+  const dim3 grid((Dv + cols - 1) / cols, H, n_seqs), block(kScanThreads);
+  if (grid.y > 65535 || grid.z > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (dtype == LLMIE_F32)
+    launch_k(matrix_scan_kernel<float>, grid, block, 0, stream, qa, fg, (const float*)v, v_ld, state, cu_q, seq_slot, o,
+             H, D, Dv, S, R, write_state);
+  else if (dtype == LLMIE_BF16)
+    launch_k(matrix_scan_kernel<__nv_bfloat16>, grid, block, 0, stream, qa, fg, (const __nv_bfloat16*)v, v_ld, state,
+             cu_q, seq_slot, o, H, D, Dv, S, R, write_state);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// o float32 [n_items, Dv] (an item = a token's head); w float32 [Dv]; y [n_items, Dv] of `dtype`.
+extern "C" int llmie_head_rmsnorm(const float* o, const float* w, float eps, void* y, long long n_items, int Dv,
+                                  int dtype, cudaStream_t stream) {
+  if (n_items < 0 || Dv <= 0) return LLMIE_ERR_BAD_ARG;
+  if (n_items == 0) return LLMIE_OK;
+  const int warps = 4;
+  const long long blocks = (n_items + warps - 1) / warps;
+  if (blocks > 0x7fffffffLL) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  const dim3 grid((unsigned)blocks), block(warps * 32);
+  if (dtype == LLMIE_F32)
+    launch_k(head_rmsnorm_kernel<float>, grid, block, 0, stream, o, w, eps, (float*)y, Dv, (size_t)n_items);
+  else if (dtype == LLMIE_BF16)
+    launch_k(head_rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, stream, o, w, eps, (__nv_bfloat16*)y, Dv,
+             (size_t)n_items);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// proj [T, ld] of `dtype` with the convolution's input at column x_off (C columns); x_bias, conv_bias float32 [C] or
+// null; taps float32 [C, K] (the last column multiplies the current token); conv_state float32 [slots, K-1, C];
+// u float32 [T, C].
+extern "C" int llmie_causal_conv(const void* proj, int ld, int x_off, const float* x_bias, const float* taps,
+                                 const float* conv_bias, const float* conv_state, const int* cu_q, const int* tok_seq,
+                                 const int* seq_slot, float* u, int n_tokens, int C, int K, int dtype,
+                                 cudaStream_t stream) {
+  if (n_tokens < 0 || C <= 0 || K <= 0 || x_off < 0 || ld < x_off + C) return LLMIE_ERR_BAD_ARG;
+  if (K > kMaxTaps) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t total = (size_t)n_tokens * C;
+  const dim3 grid(sweep_blocks(total, 256)), block(256);
+  if (dtype == LLMIE_F32)
+    launch_k(causal_conv_kernel<float>, grid, block, 0, stream, (const float*)proj, ld, x_off, x_bias, taps, conv_bias,
+             conv_state, cu_q, tok_seq, seq_slot, u, C, K, total);
+  else if (dtype == LLMIE_BF16)
+    launch_k(causal_conv_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)proj, ld, x_off, x_bias,
+             taps, conv_bias, conv_state, cu_q, tok_seq, seq_slot, u, C, K, total);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// gates float32 [T, 2 C] (per group of bw channels: r's pre-activations, then i's), changed in place into (a, drive);
+// u float32 [T, C]; r_bias, i_bias, lam float32 [C].
+extern "C" int llmie_unit_gate_values(float* gates, const float* u, const float* r_bias, const float* i_bias,
+                                      const float* lam, float c_decay, int n_tokens, int C, int bw,
+                                      cudaStream_t stream) {
+  if (n_tokens < 0 || C <= 0 || bw <= 0 || C % bw) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t total = (size_t)n_tokens * C;
+  launch_k(unit_gate_values_kernel, dim3(sweep_blocks(total, 256)), dim3(256), 0, stream, gates, u, r_bias, i_bias, lam,
+           c_decay, C, bw, total);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// gates as left by llmie_unit_gate_values; proj [T, ld] of `dtype` with the output gate's raw projection at y_off and
+// the convolution's input at x_off; state float32 [slots, C]; conv_state float32 [slots, K-1, C]; out [T, C] of `dtype`.
+extern "C" int llmie_unit_scan(const float* gates, const void* proj, int ld, int y_off, int x_off, const float* y_bias,
+                               const float* x_bias, int act, float* state, float* conv_state, const int* cu_q,
+                               const int* seq_slot, void* out, int n_seqs, int C, int bw, int K, int write_state,
+                               int dtype, cudaStream_t stream) {
+  if (n_seqs < 0 || C <= 0 || bw <= 0 || C % bw || K <= 0 || y_off < 0 || x_off < 0 || ld < y_off + C || ld < x_off + C)
+    return LLMIE_ERR_BAD_ARG;
+  if (act < 0 || act > 4) return LLMIE_ERR_BAD_ARG;
+  if (K > kMaxTaps) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (n_seqs == 0) return LLMIE_OK;
+  if (n_seqs > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  const int threads = C >= 128 ? 128 : ((C + 31) / 32) * 32;
+  const dim3 grid((C + threads - 1) / threads, n_seqs), block(threads);
+  if (dtype == LLMIE_F32)
+    launch_k(unit_scan_kernel<float>, grid, block, 0, stream, gates, (const float*)proj, ld, y_off, x_off, y_bias,
+             x_bias, act, state, conv_state, cu_q, seq_slot, (float*)out, C, bw, K, write_state);
+  else if (dtype == LLMIE_BF16)
+    launch_k(unit_scan_kernel<__nv_bfloat16>, grid, block, 0, stream, gates, (const __nv_bfloat16*)proj, ld, y_off,
+             x_off, y_bias, x_bias, act, state, conv_state, cu_q, seq_slot, (__nv_bfloat16*)out, C, bw, K, write_state);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}

@@ -66,4 +66,5 @@ class StepContext:
             return
         ops.attention_paged(q, kv.k, kv.v, out, self.tok_pos, self.tok_seq, self.seq_slot, kv.block_table,
                             kv.page_size, n_q, n_kv, head_dim, options.scale, options.window, options.keep_first,
-                            options.sink, gate, options.softcap, options.distance_bias, options.sink_values)
+                            options.sink, gate, options.softcap, options.distance_bias, options.sink_values,
+                            options.sigmoid_bias)

@@ -57,6 +57,8 @@ class KernelPlan:
         every option (scale, window, kept first keys, sink, gate); the CUDA-core split-KV kernel knows scale and
         window. A value head size that differs from the key head size is the plain kernel's alone."""
         scale, window = options.scale, options.window
+        if options.sigmoid_bias is not None:
+            return self._sigmoid_attention(ctx, q, kv, out, n_q, n_kv, head_dim, options, gate)
         if kv.v.shape[-1] != head_dim or not kv.v.is_contiguous():
             # a value size of its own, or values that are columns of the key rows (a latent)
             return self._attention_by_rows(ctx, q, kv, out, n_q, n_kv, head_dim, options, gate)
@@ -97,6 +99,10 @@ class KernelPlan:
             if gate is not None:
                 ops.sigmoid_gate(out, gate)
             return True
+        return False
+
+    def _sigmoid_attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, options, gate) -> bool:
+        """Attention without a softmax (weights sigmoid(score + a number per head), not normalised)."""
         return False
 
     def _attention_by_rows(self, ctx, q, kv, out, n_q, n_kv, head_dim, options, gate) -> bool:

@@ -31,6 +31,8 @@ FAMILIES: Dict[str, tuple] = {
     "elementwise": ("elementwise.cu", [], []),
     "branch_elementwise": ("branch_elementwise.cu", [], []),
     "parallel_elementwise": ("parallel_elementwise.cu", [], []),
+    "scaled_elementwise": ("scaled_elementwise.cu", [], []),
+    "recurrent": ("recurrent.cu", [], []),
     "grouped_gemm": ("grouped_gemm.cu", [], []),
     "moe": ("moe.cu", [], []),
     "latent": ("latent.cu", [], []),

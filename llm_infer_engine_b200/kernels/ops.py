@@ -219,14 +219,17 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 
 def rope_store(qkv, q_out, k_cache, v_cache, table, tok_pos, tok_seq, seq_slot, block_table, page_size: int,
-               n_q: int, n_kv: int, head_dim: int, rot_dim: int, write_kv: bool = True):
+               n_q: int, n_kv: int, head_dim: int, rot_dim: int, write_kv: bool = True,
+               v_head_dim: Optional[int] = None):
     """Rotates q and k by position and writes k, v into the paged cache.
 
-    qkv [T, (n_q + 2 n_kv) hd]; q_out [T, n_q hd]; caches [n_pages, n_kv, page_size, hd] (same dtype);
+    qkv [T, (n_q + n_kv) hd + n_kv hdv]; q_out [T, n_q hd]; caches [n_pages, n_kv, page_size, hd] (same dtype), the
+    value cache with hdv (`v_head_dim`, default hd) in place of hd;
     table float32 [max_pos, rot_dim / 2, 2] of (cos, sin) or None for no rotation;
     tok_pos, tok_seq int32 [T]; seq_slot int32 [n]; block_table int32 [n_slots, max_pages]."""
     T = qkv.shape[0]
-    _need(qkv, "qkv", None, (T, (n_q + 2 * n_kv) * head_dim))
+    hdv = head_dim if v_head_dim is None else int(v_head_dim)
+    _need(qkv, "qkv", None, (T, (n_q + n_kv) * head_dim + n_kv * hdv))
     _need(q_out, "q_out", qkv.dtype, (T, n_q * head_dim))
     _need(tok_pos, "tok_pos", torch.int32)
     _need(tok_seq, "tok_seq", torch.int32)
@@ -240,21 +243,22 @@ def rope_store(qkv, q_out, k_cache, v_cache, table, tok_pos, tok_seq, seq_slot, 
         table_len = table.shape[0]
     if write_kv:
         _need(k_cache, "k_cache", qkv.dtype, (None, n_kv, page_size, head_dim))
-        _need(v_cache, "v_cache", qkv.dtype, tuple(k_cache.shape))
-    _work(_nbytes(qkv, q_out) + (2 * T * n_kv * head_dim * qkv.element_size() if write_kv else 0))
-    f = _fn("elementwise", "llmie_rope_store",
-            [_c_void_p] * 9 + [_c_int] * 10 + [_c_void_p])
+        _need(v_cache, "v_cache", qkv.dtype, tuple(k_cache.shape[:-1]) + (hdv,))
+    _work(_nbytes(qkv, q_out) + (T * n_kv * (head_dim + hdv) * qkv.element_size() if write_kv else 0))
+    f = _fn("elementwise", "llmie_rope_store_ex",
+            [_c_void_p] * 9 + [_c_int] * 11 + [_c_void_p])
     _check(f(qkv.data_ptr(), q_out.data_ptr(), _ptr(k_cache) if write_kv else None,
              _ptr(v_cache) if write_kv else None, _ptr(table), tok_pos.data_ptr(), tok_seq.data_ptr(),
              seq_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, T, n_q,
-             n_kv, head_dim, rot_dim, table_len, 1 if write_kv else 0, _dt(qkv, "qkv"), _stream()), "rope_store")
+             n_kv, head_dim, hdv, rot_dim, table_len, 1 if write_kv else 0, _dt(qkv, "qkv"), _stream()), "rope_store")
     return q_out
 
 
 def attention_paged(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_table, page_size: int,
                     n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0, keep_first: int = 0,
                     sink: bool = False, gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                    dist_bias: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None):
+                    dist_bias: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None,
+                    sigmoid_bias: Optional[torch.Tensor] = None):
     """Plain attention over the paged cache, one warp per (token, query head).
     q [T, n_q hd]; out [T, n_q hdv]; k_cache [n_pages, n_kv, page_size, hd]; v_cache the same with hdv (the value
     head size, read from its shape). window 0 = all earlier keys; the first `keep_first` keys of a sequence stay
@@ -263,7 +267,8 @@ def attention_paged(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_
     turns a scaled score s into c tanh(s / c); `dist_bias` (float32 [n_q, L]) adds a number per head and distance
     (query position - key position; distances >= L - 1 share the last column), after the cap and unscaled;
     `sink_values` (float32 [n_q]) are the sink's score per head instead of 0. v_cache may be a view of the first hdv
-    columns of k_cache's rows (a latent that is key and value at once)."""
+    columns of k_cache's rows (a latent that is key and value at once). `sigmoid_bias` (float32 [n_q]): no softmax;
+    a visible key's weight is sigmoid(score + sigmoid_bias[head]), not normalised over the keys."""
     T = q.shape[0]
     hdv = v_cache.shape[-1]
     _need(q, "q", None, (T, n_q * head_dim))
@@ -290,19 +295,23 @@ def attention_paged(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_
     if sink_values is not None:
         _need(sink_values, "sink_values", torch.float32, (n_q,))
         sink = True
+    if sigmoid_bias is not None:
+        _need(sigmoid_bias, "sigmoid_bias", torch.float32, (n_q,))
+        if sink:
+            raise KernelError("attention_paged: sigmoid weights have no denominator for a sink to enter")
     gate_ld = 0
     if gate is not None:
         gate_ld = _row_slice(gate, "gate", q.dtype, T, n_q * hdv)
     _work(2 * _nbytes(q) + 1.0 * STEP_HINT["kv_total"] * n_kv * (head_dim + hdv) * q.element_size(),
           2.0 * n_q * (head_dim + hdv) * STEP_HINT["pairs"])
-    f = _fn("attention_simt", "llmie_attention_paged_ex",
+    f = _fn("attention_simt", "llmie_attention_paged_sig",
             [_c_void_p] * 8 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_float,
-                                              _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p])
+                                              _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tok_pos.data_ptr(),
              tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, T,
              n_q, n_kv, head_dim, hdv, float(scale), int(window), int(keep_first), 1 if sink else 0, _ptr(gate),
-             gate_ld, int(v_ld), float(softcap or 0.0), _ptr(dist_bias), bias_len, _ptr(sink_values), _dt(q, "q"),
-             _stream()), "attention_paged")
+             gate_ld, int(v_ld), float(softcap or 0.0), _ptr(dist_bias), bias_len, _ptr(sink_values),
+             _ptr(sigmoid_bias), _dt(q, "q"), _stream()), "attention_paged")
     return out
 
 
@@ -1225,10 +1234,12 @@ def routed_gemm_nt(a, a_rows, w, out, out_rows, tile_group, n_positions: int, sm
 
 
 # ------------------------------------------------------------------------------------------ routed feed-forward
-def moe_route(x, w, bias, ids, weights):
+def moe_route(x, w, bias, ids, weights, scores_over_all: bool = False, correction=None, out_scale: float = 1.0):
     """Router of a mixture of experts: logits = x @ w^T + bias in float32; ids int32 [T, top] receive the `top`
     largest (ties: the lower index), weights float32 [T, top] the softmax over those logits alone.
-    x [T, d] float32 or bfloat16; w float32 [E, d]; bias float32 [E] or None."""
+    x [T, d] float32 or bfloat16; w float32 [E, d]; bias float32 [E] or None.
+    `scores_over_all`: the scores are the softmax over ALL logits, the choice goes by score + correction (float32 [E]
+    or None) and the weights are the chosen scores / (their sum + 1e-20) * out_scale."""
     T, d = x.shape
     E = w.shape[0]
     top = ids.shape[1]
@@ -1238,11 +1249,13 @@ def moe_route(x, w, bias, ids, weights):
         _need(bias, "bias", torch.float32, (E,))
     _need(ids, "ids", torch.int32, (T, top))
     _need(weights, "weights", torch.float32, (T, top))
+    if correction is not None:
+        _need(correction, "correction", torch.float32, (E,))
     _work(_nbytes(x, w, ids, weights), 2.0 * T * E * d)
-    f = _fn("moe", "llmie_moe_route", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p] + [_c_int] * 4 +
-            [_c_void_p])
+    f = _fn("moe", "llmie_moe_route_ex", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p] + [_c_int] * 5 +
+            [_c_void_p, _c_float, _c_void_p])
     _check(f(x.data_ptr(), _dt(x, "x"), w.data_ptr(), _ptr(bias), ids.data_ptr(), weights.data_ptr(), T, d, E, top,
-             _stream()), "moe_route")
+             1 if scores_over_all else 0, _ptr(correction), float(out_scale), _stream()), "moe_route")
 
 
 def moe_max_tiles(n_pairs: int, n_experts: int, tile: int) -> int:
@@ -1289,6 +1302,27 @@ def moe_combine(y, weights, shared_out, out, pair_pos=None):
     _check(f(y.data_ptr(), _dt(y, "y"), _ptr(pair_pos), weights.data_ptr(), _ptr(shared_out),
              _dt(shared_out, "shared_out") if shared_out is not None else 0, out.data_ptr(), T, d, top, _stream()),
            "moe_combine")
+    return out
+
+
+def moe_combine_identity(y, weights, ids, n_real: int, x, out, pair_pos=None):
+    """The combine for routers some of whose outputs stand for experts that return their input: a choice with
+    ids[t, k] >= n_real adds weights[t, k] * x[t] and has no row in y; the others as in `moe_combine`.
+    ids int32 [T, top]; x [T, d] float32 or bfloat16."""
+    T, top = weights.shape
+    d = out.shape[1]
+    _need(y, "y", None, (None if pair_pos is not None else T * top, d))
+    _need(weights, "weights", torch.float32)
+    _need(ids, "ids", torch.int32, (T, top))
+    _need(x, "x", None, (T, d))
+    _need(out, "out", torch.float32, (T, d))
+    if pair_pos is not None:
+        _need(pair_pos, "pair_pos", torch.int32, (T * top,))
+    _work(T * top * d * y.element_size() + _nbytes(weights, x, out))
+    f = _fn("moe", "llmie_moe_combine_identity", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                                                  _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(y.data_ptr(), _dt(y, "y"), _ptr(pair_pos), weights.data_ptr(), ids.data_ptr(), int(n_real), x.data_ptr(),
+             _dt(x, "x"), out.data_ptr(), T, d, top, _stream()), "moe_combine_identity")
     return out
 
 
@@ -1410,4 +1444,173 @@ def attention_rows_mma(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, bloc
              seq_start.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n_seqs, max_q_len, n_q, n_kv,
              head_dim, hdv, int(v_ld), 1 if shared_rows else 0, float(scale), int(window), float(softcap or 0.0),
              _ptr(dist_bias), bias_len, _ptr(sink_values), 1 if sink else 0, _stream()), "attention_rows_mma")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ scaled branches, PolyNorm
+def scaled_add_rmsnorm(h, d1, c1: float, d2, c2: float, scale, weight, eps: float, out, rows=None):
+    """h += scale (.) (c1 d1 + c2 d2) (float32, in place, when rows is None); out = rmsnorm(h) * weight.
+    h float32 [T, d]; d1, d2 [T, d] float32 or bfloat16 (d2 or both may be None); scale float32 [d] or None; weight
+    float32 [d] with out [n_out, d], or both None (the add alone). With `rows` (int32 [n_out]) only those rows are
+    produced and h stays as it is."""
+    T, d = h.shape
+    n_out = T if rows is None else rows.shape[0]
+    _need(h, "h", torch.float32)
+    for name, t in (("d1", d1), ("d2", d2)):
+        if t is not None:
+            _need(t, name, None, (T, d))
+    if scale is not None:
+        _need(scale, "scale", torch.float32, (d,))
+    if (weight is None) != (out is None):
+        raise KernelError("scaled_add_rmsnorm: weight and out go together")
+    if out is not None:
+        _need(weight, "weight", torch.float32, (d,))
+        _need(out, "out", None, (n_out, d))
+    if rows is not None:
+        _need(rows, "rows", torch.int32, (n_out,))
+        if n_out == 0:
+            return out                   # no row is wanted and h stays as it is
+    _work((2 * _nbytes(h) if rows is None else n_out * d * 4) + _nbytes(d1, d2, out))
+    f = _fn("scaled_elementwise", "llmie_scaled_add_rmsnorm",
+            [_c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p, _c_float,
+             _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
+    _check(f(h.data_ptr(), _ptr(d1), _dt(d1, "d1") if d1 is not None else 0, float(c1), _ptr(d2),
+             _dt(d2, "d2") if d2 is not None else 0, float(c2), _ptr(scale), _ptr(weight), float(eps), _ptr(out),
+             _dt(out, "out") if out is not None else 0, _ptr(rows), n_out, d, _stream()), "scaled_add_rmsnorm")
+    return out
+
+
+def poly_norm(z, coef, eps: float, out):
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(t) = t / sqrt(mean(t^2) + eps); coef float32 [4] = (a, b, c, e)
+    on the device; z, out [T, n] of one dtype; float32 arithmetic."""
+    T, n = z.shape
+    _need(z, "z")
+    _need(out, "out", z.dtype, (T, n))
+    _need(coef, "coef", torch.float32, (4,))
+    _work(_nbytes(z, out))
+    f = _fn("scaled_elementwise", "llmie_poly_norm", [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_int,
+                                                      _c_void_p])
+    _check(f(z.data_ptr(), coef.data_ptr(), float(eps), out.data_ptr(), T, n, _dt(z, "z"), _stream()), "poly_norm")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ recurrent mixers
+def matrix_gates(proj, q_off: int, f_off: int, f_bias, lower, q_out, f_out):
+    """q_out = silu(proj[:, q_off : q_off + n]); f_out = lower + (1 - lower) sigmoid(proj[:, f_off : f_off + n] + f_bias).
+    proj [T, ld] float32 or bfloat16; f_bias, lower float32 [n]; q_out, f_out float32 [T, n]."""
+    T, n = q_out.shape
+    _need(proj, "proj", None, (T, None))
+    _need(f_bias, "f_bias", torch.float32, (n,))
+    _need(lower, "lower", torch.float32, (n,))
+    _need(q_out, "q_out", torch.float32)
+    _need(f_out, "f_out", torch.float32, (T, n))
+    _work(2 * T * n * proj.element_size() + _nbytes(q_out, f_out))
+    f = _fn("recurrent", "llmie_matrix_gates", [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                                _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(proj.data_ptr(), proj.shape[1], int(q_off), int(f_off), f_bias.data_ptr(), lower.data_ptr(),
+             q_out.data_ptr(), f_out.data_ptr(), T, n, _dt(proj, "proj"), _stream()), "matrix_gates")
+
+
+def matrix_scan(q, f, v, state, cu_q, seq_slot, out, n_seqs: int, heads: int, dim: int, vdim: int,
+                write_state: bool = True):
+    """Per sequence and head, from the state S [dim, vdim] the slot holds: S <- diag(f_t) S + (1 - f_t) v_t^T and
+    out_t = S^T q_t for each of the step's tokens in order; the new S is written back. q, f float32 [T, heads dim];
+    v [T, heads vdim] (possibly a column slice) float32 or bfloat16; state float32 [slots, heads, dim, vdim];
+    out float32 [T, heads vdim]."""
+    T = q.shape[0]
+    _need(q, "q", torch.float32, (T, heads * dim))
+    _need(f, "f", torch.float32, (T, heads * dim))
+    _need(state, "state", torch.float32, (None, heads, dim, vdim))
+    _need(out, "out", torch.float32, (T, heads * vdim))
+    _need(cu_q, "cu_q", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32)
+    v_ld = _row_slice(v, "v", v.dtype, T, heads * vdim)
+    _work(_nbytes(q, f, out) + T * heads * vdim * v.element_size() + 2.0 * n_seqs * heads * dim * vdim * 4,
+          4.0 * T * heads * dim * vdim)
+    f_ = _fn("recurrent", "llmie_matrix_scan", [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                                _c_void_p] + [_c_int] * 6 + [_c_void_p])
+    _check(f_(q.data_ptr(), f.data_ptr(), v.data_ptr(), v_ld, state.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(),
+              out.data_ptr(), n_seqs, heads, dim, vdim, 1 if write_state else 0, _dt(v, "v"), _stream()), "matrix_scan")
+    return out
+
+
+def head_rmsnorm(o, weight, eps: float, out, vdim: int):
+    """out = o / sqrt(mean(o^2) + eps) * weight over every run of vdim columns (a head); o float32 [T, heads vdim];
+    weight float32 [vdim]; out of the activation type."""
+    T, n = o.shape
+    _need(o, "o", torch.float32)
+    _need(weight, "weight", torch.float32, (vdim,))
+    _need(out, "out", None, (T, n))
+    if n % vdim:
+        raise KernelError("head_rmsnorm: the row is not a whole number of heads")
+    _work(_nbytes(o, out))
+    f = _fn("recurrent", "llmie_head_rmsnorm", [_c_void_p, _c_void_p, _c_float, _c_void_p, ctypes.c_longlong, _c_int,
+                                                _c_int, _c_void_p])
+    _check(f(o.data_ptr(), weight.data_ptr(), float(eps), out.data_ptr(), T * (n // vdim), vdim, _dt(out, "out"),
+             _stream()), "head_rmsnorm")
+    return out
+
+
+def causal_conv(proj, x_off: int, x_bias, taps, conv_bias, conv_state, cu_q, tok_seq, seq_slot, out):
+    """out[t, c] = conv_bias[c] + sum_j taps[c, K-1-j] x[t-j, c] with x = proj[:, x_off + c] + x_bias[c]; inputs from
+    before the step are the slot's conv_state (its last K-1 inputs, zeros at a sequence's start).
+    taps float32 [C, K]; conv_state float32 [slots, K-1, C]; out float32 [T, C]."""
+    T, C = out.shape
+    K = taps.shape[1]
+    _need(proj, "proj", None, (T, None))
+    _need(taps, "taps", torch.float32, (C, K))
+    _need(conv_state, "conv_state", torch.float32, (None, K - 1, C))
+    _need(out, "out", torch.float32)
+    for name, t in (("x_bias", x_bias), ("conv_bias", conv_bias)):
+        if t is not None:
+            _need(t, name, torch.float32, (C,))
+    for name, t in (("cu_q", cu_q), ("tok_seq", tok_seq), ("seq_slot", seq_slot)):
+        _need(t, name, torch.int32)
+    _work(T * C * (proj.element_size() + 4))
+    f = _fn("recurrent", "llmie_causal_conv", [_c_void_p, _c_int, _c_int] + [_c_void_p] * 8 + [_c_int] * 4 + [_c_void_p])
+    _check(f(proj.data_ptr(), proj.shape[1], int(x_off), _ptr(x_bias), taps.data_ptr(), _ptr(conv_bias),
+             conv_state.data_ptr(), cu_q.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), out.data_ptr(), T, C, K,
+             _dt(proj, "proj"), _stream()), "causal_conv")
+    return out
+
+
+def unit_gate_values(gates, u, r_bias, i_bias, lam, c_decay: float, block_width: int):
+    """gates float32 [T, 2 C], per group of block_width channels the pre-activations of r and then of i, become in place
+    a = exp(-c_decay sigmoid(r + r_bias) softplus(lam)) and sqrt(1 - a^2) sigmoid(i + i_bias) u. u float32 [T, C]."""
+    T, C = u.shape
+    _need(u, "u", torch.float32)
+    _need(gates, "gates", torch.float32, (T, 2 * C))
+    for name, t in (("r_bias", r_bias), ("i_bias", i_bias), ("lam", lam)):
+        _need(t, name, torch.float32, (C,))
+    _work(2 * _nbytes(gates) + _nbytes(u))
+    f = _fn("recurrent", "llmie_unit_gate_values", [_c_void_p] * 5 + [_c_float, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(gates.data_ptr(), u.data_ptr(), r_bias.data_ptr(), i_bias.data_ptr(), lam.data_ptr(), float(c_decay), T, C,
+             int(block_width), _stream()), "unit_gate_values")
+
+
+def unit_scan(gates, proj, y_off: int, x_off: int, y_bias, x_bias, act: int, state, conv_state, cu_q, seq_slot, out,
+              n_seqs: int, block_width: int, write_state: bool = True):
+    """Per sequence and channel, from the slot's state S: S <- a_t S + drive_t, out_t = S * act(proj[t, y_off + c] +
+    y_bias[c]) for the step's tokens in order (gates as `unit_gate_values` leaves them); the new S and the last K-1
+    inputs of the convolution (proj[:, x_off + c] + x_bias) are written back. state float32 [slots, C]; conv_state
+    float32 [slots, K-1, C]; out [T, C] of proj's dtype."""
+    T, C = out.shape
+    K = conv_state.shape[1] + 1
+    _need(gates, "gates", torch.float32, (T, 2 * C))
+    _need(proj, "proj", None, (T, None))
+    _need(out, "out", proj.dtype)
+    _need(state, "state", torch.float32, (None, C))
+    _need(conv_state, "conv_state", torch.float32, (state.shape[0], K - 1, C))
+    for name, t in (("y_bias", y_bias), ("x_bias", x_bias)):
+        if t is not None:
+            _need(t, name, torch.float32, (C,))
+    _need(cu_q, "cu_q", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32)
+    _work(_nbytes(gates, out) + T * C * proj.element_size())
+    f = _fn("recurrent", "llmie_unit_scan", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
+                                             _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p] + [_c_int] * 6 +
+            [_c_void_p])
+    _check(f(gates.data_ptr(), proj.data_ptr(), proj.shape[1], int(y_off), int(x_off), _ptr(y_bias), _ptr(x_bias),
+             int(act), state.data_ptr(), conv_state.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(), out.data_ptr(),
+             n_seqs, C, int(block_width), K, 1 if write_state else 0, _dt(proj, "proj"), _stream()), "unit_scan")
     return out

@@ -1,4 +1,4 @@
-from . import dofipel, llama, zemivik  # noqa: F401  (register LlamaForCausalLM, Zemivik and Dofipel)
+from . import dofipel, ganupel, llama, zemivik  # noqa: F401  (register LlamaForCausalLM, Zemivik, Dofipel, Ganupel)
 from .decoder import DecoderModel
 
 __all__ = ["DecoderModel"]

@@ -63,11 +63,14 @@ class AttentionOptions:
     # float32 [query heads, L]: a number per head and distance (query position - key position) added to the score
     # after the cap, unscaled; distances of L - 1 and more share the last column
     distance_bias: Optional[torch.Tensor] = None
+    # float32 [query heads]: no softmax at all; a visible key's weight is sigmoid(score + this number of its head), and
+    # the weights are not normalised over the keys (so there is no denominator for a sink to enter)
+    sigmoid_bias: Optional[torch.Tensor] = None
 
     @property
     def plain(self) -> bool:
         """Only the options every attention kernel knows (scale, window)."""
-        return self.keep_first == 0 and not self.sink and not self.scored
+        return self.keep_first == 0 and not self.sink and not self.scored and self.sigmoid_bias is None
 
     @property
     def scored(self) -> bool:
@@ -112,9 +115,41 @@ class Norm(Part):
         return None
 
 
+class ScaledDelta:
+    """Branch output that is scaled on its way into the stream: vector (.) (c1 t1 + c2 t2), with `terms` a list of
+    one or two (tensor, constant) pairs and `vector` a float32 [d] scale per channel or None. A mixer made of two
+    mixers returns one without a vector; a block with a learned scale per channel puts its vector on whatever its
+    branch returned. A norm whose kernel knows the form adds it while it reads the stream; `materialize()` gives the
+    plain float32 tensor to everything else."""
+
+    def __init__(self, terms, vector: Optional[torch.Tensor] = None):
+        terms = [(t, float(c)) for t, c in terms]
+        if not 1 <= len(terms) <= 2:
+            raise ValueError("a ScaledDelta has one or two terms")
+        self.terms, self.vector = terms, vector
+
+    @staticmethod
+    def of(y, vector: Optional[torch.Tensor]) -> "ScaledDelta":
+        """`y` (a tensor or a ScaledDelta without a vector) times `vector`, channel by channel."""
+        if isinstance(y, ScaledDelta):
+            if y.vector is not None:
+                raise ValueError("this branch output already carries a vector")
+            return ScaledDelta(y.terms, vector)
+        return ScaledDelta([(y, 1.0)], vector)
+
+    def materialize(self) -> torch.Tensor:
+        from ..kernels import ops
+        (t1, c1), (t2, c2) = self.terms[0], (self.terms[1] if len(self.terms) > 1 else (None, 0.0))
+        out = torch.zeros(t1.shape, dtype=torch.float32, device=t1.device)
+        ops.scaled_add_rmsnorm(out, t1, c1, t2, c2, self.vector, None, 0.0, None)
+        return out
+
+
 def single_delta(delta):
     """One tensor for norms whose kernel adds one: the members of a tuple are summed into a float32 member (or a
-    float32 copy of the first) by the residual-add kernel."""
+    float32 copy of the first) by the residual-add kernel; a ScaledDelta is worked out."""
+    if isinstance(delta, ScaledDelta):
+        return delta.materialize()
     if not isinstance(delta, (tuple, list)):
         return delta
     parts = [d for d in delta if d is not None]

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops, trace
-from .base import Block, DeferredBranchAdd, call_branch, register_block
+from .base import Block, DeferredBranchAdd, ScaledDelta, call_branch, register_block
 
 
 class PreNormBlock(Block):
@@ -173,3 +173,41 @@ class ParallelMixerBlock(Block):
 
 register_block("parallel", ParallelBlock)
 register_block("parallel_mixer", ParallelMixerBlock)
+
+
+class PreNormScaledBlock(Block):
+    """h += s1 (.) mixer(norm(h)); h += s2 (.) feed_forward(norm(h)): the pre-norm block with a learned scale per
+    channel on each branch's output (the roles `mixer_scale` and `feed_forward_scale`, pointwise parts of kind
+    "layer_scale"). The scaled output travels to the next norm as a `ScaledDelta`, whose kernel multiplies and adds
+    while it reads the stream, so the scale costs no launch; a mixer made of two mixers hands over both outputs with
+    their constants and they are added in the same pass."""
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm",
+             "mixer_scale": "pointwise", "feed_forward_scale": "pointwise"}
+
+    def forward(self, h, pending, ctx, unit, owns_cache):
+        tracing = trace.active()
+        if tracing:
+            trace.push(f"Attn_{ctx.entry}")
+        x = self.mixer_norm.forward(h, pending)
+        mixed = ScaledDelta.of(call_branch(self.mixer, x, ctx, unit, owns_cache), self.mixer_scale.vector)
+        if tracing:
+            trace.pop()
+            trace.push(f"FFN_{ctx.entry}")
+        x = self.feed_forward_norm.forward(h, mixed)
+        out = ScaledDelta.of(call_branch(self.feed_forward, x, ctx), self.feed_forward_scale.vector)
+        if tracing:
+            trace.pop()
+        return h, out
+
+
+class PreNormScaledMixerBlock(Block):
+    """The same arrangement for a layer without a feed-forward: h += s1 (.) mixer(norm(h))."""
+    ROLES = {"mixer": "mixer", "mixer_norm": "norm", "mixer_scale": "pointwise"}
+
+    def forward(self, h, pending, ctx, unit, owns_cache):
+        x = self.mixer_norm.forward(h, pending)
+        return h, ScaledDelta.of(call_branch(self.mixer, x, ctx, unit, owns_cache), self.mixer_scale.vector)
+
+
+register_block("pre_norm_scaled", PreNormScaledBlock)
+register_block("pre_norm_scaled_mixer", PreNormScaledMixerBlock)

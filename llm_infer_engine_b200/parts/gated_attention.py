@@ -26,6 +26,10 @@ Three more options change single scores, each off by default:
                                              per distance nearby, rows evenly spaced in log(distance) up to `far`
                                              beyond, the last row for everything farther; added after the cap, unscaled
     sink = "learned"                         the sink's score is a learned number per head instead of 0
+
+Two more, also off by default: `position` (a position encoding, e.g. rotary: q and k are encoded before the scores and
+keys are cached encoded; it takes the place of the query/key norm) and `weights = "sigmoid"`: no softmax, a visible
+key's weight is sigmoid(s_ij + b_head) with a learned number per head, and nothing is normalised over the keys.
 """
 from __future__ import annotations
 
@@ -36,11 +40,11 @@ import torch
 
 from ..cache.cache import KVRequest
 from ..kernels import ops, trace
-from .base import AttentionOptions, DeferredBranchAdd, Mixer, ParamSpec, register_mixer
+from .base import AttentionOptions, DeferredBranchAdd, Mixer, ParamSpec, build_part, register_mixer
 from .linear import Linear
 
 _DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm",
-                  "blend": "vmix", "distance_bias": "rel", "sink": "sink"}
+                  "blend": "vmix", "distance_bias": "rel", "sink": "sink", "sigmoid_bias": "pb"}
 
 
 RANDOM_BIAS_ROWS = 16
@@ -67,7 +71,8 @@ class GatedAttention(Mixer):
     earlier key), keep_first, sink (bool), qk_norm_eps (None = no query/key norm), gate (bool), value_blend
     (None, "first": leaves its projected values for later layers, or "blend": mixes them into its own),
     blend_key (name under which the first layer's values travel through the step), names (overrides of the
-    tensors' checkpoint sub-names)."""
+    tensors' checkpoint sub-names), position (PartSpec of a position encoding for q and k, None = none), weights
+    ("softmax", the default, or "sigmoid")."""
 
     accepts_deferred_branch_add = True
 
@@ -95,6 +100,14 @@ class GatedAttention(Mixer):
                                         window=self.window, keep_first=self.keep_first, sink=bool(p.get("sink", False)),
                                         softcap=self.softcap)
         self.qk_norm_eps = p.get("qk_norm_eps")
+        self.position = build_part("position_encoding", p["position"], runtime) if p.get("position") else None
+        if self.position is not None and (self.qk_norm_eps is not None or p.get("value_blend")):
+            raise ValueError("a position encoding takes the place of the query/key norm and the value blend")
+        self.sigmoid = p.get("weights", "softmax") == "sigmoid"
+        if p.get("weights", "softmax") not in ("softmax", "sigmoid"):
+            raise ValueError(f"weights must be 'softmax' or 'sigmoid', got {p.get('weights')!r}")
+        if self.sigmoid and (p.get("sink") or self.softcap or self.distance_bias is not None or self.keep_first):
+            raise ValueError("sigmoid weights go with scale and window only")
         self.gate = bool(p.get("gate", False))
         self.value_blend = p.get("value_blend")
         if self.value_blend not in (None, "first", "blend"):
@@ -122,6 +135,8 @@ class GatedAttention(Mixer):
                                                   role="vector", init=("uniform", -1.0, 1.0))
         if self.learned_sink:
             specs[n["sink"]] = ParamSpec((self.n_heads,), role="vector", init=("uniform", -1.0, 1.0))
+        if self.sigmoid:
+            specs[n["sigmoid_bias"]] = ParamSpec((self.n_heads,), role="vector", init=("uniform", -6.0, -2.0))
         if self.value_blend is not None:
             # only a blending layer reads the scalar; a checkpoint may hold one for the first layer as well
             specs[n["blend"]] = ParamSpec((), role="vector", init=("uniform", 0.2, 0.8),
@@ -153,6 +168,8 @@ class GatedAttention(Mixer):
             extra["distance_bias"] = table[index].t().contiguous()
         if self.learned_sink:
             extra["sink_values"] = tensors[n["sink"]].to(torch.float32).contiguous()
+        if self.sigmoid:
+            extra["sigmoid_bias"] = tensors[n["sigmoid_bias"]].to(torch.float32).contiguous()
         if extra:
             import dataclasses
             self.options = dataclasses.replace(self.options, **extra)
@@ -182,11 +199,17 @@ class GatedAttention(Mixer):
             if v_first is None:
                 raise RuntimeError(f"a layer blends its values with {self.blend_key!r}, but no earlier layer of this "
                                    "step has left any")
-        trace.push("QKnorm+KV_cache")
-        q = torch.empty((T, self.nq), dtype=proj.dtype, device=proj.device)
-        ops.qk_norm_store(proj, q, kv.k, kv.v, self.q_w, self.k_w, float(self.qk_norm_eps or 0.0), ctx.tok_pos,
-                          ctx.tok_seq, ctx.seq_slot, kv.block_table, kv.page_size, self.n_heads, self.n_kv_heads,
-                          self.head_dim, self.v_head_dim, owns_cache, lam=self.lam, v_first=v_first)
+        if self.position is not None:
+            trace.push("RoPE+KV_cache")
+            qkv = proj if not self.gate else proj[:, :self.nq + self.nk + self.nv].contiguous()
+            q = self.position.encode_and_store(qkv, ctx, kv, self.n_heads, self.n_kv_heads, self.head_dim, owns_cache,
+                                               v_head_dim=self.v_head_dim)
+        else:
+            trace.push("QKnorm+KV_cache")
+            q = torch.empty((T, self.nq), dtype=proj.dtype, device=proj.device)
+            ops.qk_norm_store(proj, q, kv.k, kv.v, self.q_w, self.k_w, float(self.qk_norm_eps or 0.0), ctx.tok_pos,
+                              ctx.tok_seq, ctx.seq_slot, kv.block_table, kv.page_size, self.n_heads, self.n_kv_heads,
+                              self.head_dim, self.v_head_dim, owns_cache, lam=self.lam, v_first=v_first)
         trace.pop()
         out = torch.empty((T, self.no), dtype=proj.dtype, device=proj.device)
         gate = proj[:, self.nq + self.nk + self.nv:] if self.gate else None

@@ -87,10 +87,14 @@ register_feed_forward("swiglu", SwiGLU)
 class DenseMLP(FeedForward):
     """down(act(up x + b_up)) + b_down: one up projection, a pointwise activation, one down projection.
 
-    params: hidden, intermediate, activation ("relu2" = the square of relu, "relu", "gelu_tanh", "silu"), bias (bool),
-    names (overrides of the checkpoint sub-names: up, up_bias, down, down_bias). The result is float32. A block
-    that adds the output bias inside its own next kernel calls `forward(..., defer_bias=True)` and reads
-    `down_bias` itself."""
+    params: hidden, intermediate, activation ("relu2" = the square of relu, "relu", "gelu_tanh", "silu", or
+    "poly_norm"), bias (bool), names (overrides of the checkpoint sub-names: up, up_bias, down, down_bias,
+    poly_norm). The result is float32. A block that adds the output bias inside its own next kernel calls
+    `forward(..., defer_bias=True)` and reads `down_bias` itself.
+
+    "poly_norm" is not pointwise: a N(z) + b N(z^2) + c N(z^3) + e over a token's whole vector z of up-projections,
+    N(t) = t / sqrt(mean(t^2) + eps) with `norm_eps` (a param), powers element by element, and a, b, c, e four learned
+    numbers stored as one tensor; float32 arithmetic."""
 
     accepts_deferred_branch_add = True
 
@@ -98,11 +102,14 @@ class DenseMLP(FeedForward):
         super().__init__(params, runtime)
         self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
         name = str(params.get("activation", "relu2"))
-        if name not in ops.ACTIVATIONS:
-            raise ValueError(f"activation {name!r} is not known ({sorted(ops.ACTIVATIONS)})")
-        self.activation = ops.ACTIVATIONS[name]
+        self.poly_norm = name == "poly_norm"
+        if not self.poly_norm and name not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {name!r} is not known ({sorted(ops.ACTIVATIONS) + ['poly_norm']})")
+        self.activation = ops.ACT_NONE if self.poly_norm else ops.ACTIVATIONS[name]
+        self.norm_eps = float(params["norm_eps"]) if self.poly_norm else 0.0
+        self.poly_coef = None
         self.bias = bool(params.get("bias", True))
-        self.names = dict({"up": "up", "up_bias": "up.b", "down": "down", "down_bias": "down.b"},
+        self.names = dict({"up": "up", "up_bias": "up.b", "down": "down", "down_bias": "down.b", "poly_norm": "act"},
                           **(params.get("names") or {}))
         self.up: Linear = None
         self.down: Linear = None
@@ -115,6 +122,8 @@ class DenseMLP(FeedForward):
         if self.bias:
             specs[n["up_bias"]] = ParamSpec((self.intermediate,), role="vector", init=("normal",))
             specs[n["down_bias"]] = ParamSpec((self.hidden,), role="vector", init=("normal",))
+        if self.poly_norm:
+            specs[n["poly_norm"]] = ParamSpec((4,), role="vector", init=("uniform", -1.0, 1.0))
         return specs
 
     def load(self, tensors):
@@ -123,6 +132,8 @@ class DenseMLP(FeedForward):
         if self.bias:
             self.up_bias = tensors[n["up_bias"]].to(torch.float32).contiguous()
             self.down_bias = tensors[n["down_bias"]].to(torch.float32).contiguous()
+        if self.poly_norm:
+            self.poly_coef = tensors[n["poly_norm"]].to(torch.float32).contiguous()
 
     def weight_bytes(self) -> int:
         return self.up.nbytes() + self.down.nbytes() + (4 * (self.intermediate + self.hidden) if self.bias else 0)
@@ -144,6 +155,8 @@ class DenseMLP(FeedForward):
                 u = self.up(x)
                 a = torch.empty_like(u)
                 ops.bias_act(u, self.up_bias, a, self.activation)
+            if self.poly_norm:
+                a = ops.poly_norm(a, self.poly_coef, self.norm_eps, torch.empty_like(a))
             y = self.down(a, out_dtype=torch.float32)
             if self.down_bias is not None and not defer_bias:
                 ops.bias_act(y, self.down_bias, y, ops.ACT_NONE)

@@ -1,7 +1,8 @@
 """RMSNorm fused with the residual add that precedes it.
 
 y = x * rsqrt(mean(x^2) + eps) * w, all in float32, one rounding at the store
-(src/rms_norm.py:32-39 of the reference). The weight is used as it is (not 1 + w).
+(src/rms_norm.py:32-39 of the reference). The weight is used as it is (not 1 + w), unless `weight_offset` says that
+the checkpoint stores the weight's distance from a constant (1 + w for an offset of 1).
 """
 from __future__ import annotations
 
@@ -10,12 +11,13 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import ops, trace
-from .base import DeferredNorm, Norm, ParamSpec, register_norm, single_delta
+from .base import DeferredNorm, Norm, ParamSpec, ScaledDelta, register_norm, single_delta
 
 
 class RMSNorm(Norm):
     """params: size (width of a row), eps; weight_name (the tensor's name under the part's checkpoint name,
-    default "weight"; "" = the part's name itself)."""
+    default "weight"; "" = the part's name itself); weight_offset (default 0: the norm multiplies by
+    weight_offset + the stored tensor, for checkpoints that store the weight around zero)."""
 
     kind = "rmsnorm"
 
@@ -24,13 +26,17 @@ class RMSNorm(Norm):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.weight_name = str(params.get("weight_name", "weight"))
+        self.weight_offset = float(params.get("weight_offset", 0.0))
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {self.weight_name: ParamSpec((self.size,), role="vector", init=tuple(self.params.get("init", ("ones",))))}
+        init = ("ones",) if not self.weight_offset else ("uniform", -0.2, 0.2)
+        return {self.weight_name: ParamSpec((self.size,), role="vector", init=tuple(self.params.get("init", init)))}
 
     def load(self, tensors):
         self.weight = tensors[self.weight_name].to(torch.float32).contiguous()   # bf16 -> f32 is exact
+        if self.weight_offset:
+            self.weight = (self.weight + self.weight_offset).contiguous()        # the sum in float32
 
     def weight_bytes(self) -> int:
         return self.size * 4
@@ -46,6 +52,12 @@ class RMSNorm(Norm):
         if out is None:
             out = torch.empty((n_out, self.size), dtype=self.runtime.dtype, device=h.device)
         trace.push("RMSNorm")
+        if isinstance(delta, ScaledDelta):
+            # a scaled branch output (or two): the add, the scales and the norm are one kernel
+            (t1, c1), (t2, c2) = delta.terms[0], (delta.terms[1] if len(delta.terms) > 1 else (None, 0.0))
+            ops.scaled_add_rmsnorm(h, t1, c1, t2, c2, delta.vector, self.weight, self.eps, out, rows)
+            trace.pop()
+            return out
         delta = single_delta(delta)
         if delta is not None and delta.dtype != out.dtype:
             # the fused kernel adds a branch output of the activations' type; any other is added by a kernel of its own

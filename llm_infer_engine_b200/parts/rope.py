@@ -44,7 +44,7 @@ def inverse_frequencies(rot_dim: int, theta: float, scaling: Optional[dict]) -> 
 class RotaryEncoding(PositionEncoding):
     """params: rot_dim (how many leading elements of a head are rotated), theta, scaling
     (None or {"rope_type": "llama3", factor, low_freq_factor, high_freq_factor,
-    original_max_position_embeddings})."""
+    original_max_position_embeddings}), exact_angles (bool: the table from double-precision angles, without scaling)."""
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
@@ -55,9 +55,16 @@ class RotaryEncoding(PositionEncoding):
         self.scaling = params.get("scaling")
         inv = inverse_frequencies(self.rot_dim, self.theta, self.scaling)
         self.inv_freq = inv
-        pos = torch.arange(runtime.max_positions, dtype=torch.float32)
-        angle = torch.outer(pos, inv).float()
-        table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1)       # [P, rot/2, 2]
+        if params.get("exact_angles"):
+            # frequencies and angles in double precision, cosine and sine rounded once to float32
+            inv64 = torch.tensor([self.theta ** (-2.0 * i / self.rot_dim) for i in range(self.rot_dim // 2)],
+                                 dtype=torch.float64)
+            angle = torch.outer(torch.arange(runtime.max_positions, dtype=torch.float64), inv64)
+            table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).float()
+        else:
+            pos = torch.arange(runtime.max_positions, dtype=torch.float32)
+            angle = torch.outer(pos, inv).float()
+            table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1)   # [P, rot/2, 2]
         self.table = table.contiguous().to(runtime.device)
 
     def fused_table(self, head_dim: int):
@@ -65,11 +72,13 @@ class RotaryEncoding(PositionEncoding):
         that needs the whole head to be rotated."""
         return self.table if self.rot_dim == head_dim else None
 
-    def encode_and_store(self, qkv, ctx, kv, n_q, n_kv, head_dim, write_kv):
+    def encode_and_store(self, qkv, ctx, kv, n_q, n_kv, head_dim, write_kv, v_head_dim=None):
+        """`v_head_dim`: the size of a value head where it differs from head_dim (the packed row then ends with
+        n_kv * v_head_dim value columns)."""
         q = torch.empty((qkv.shape[0], n_q * head_dim), dtype=qkv.dtype, device=qkv.device)
         ops.rope_store(qkv, q, kv.k if kv is not None else None, kv.v if kv is not None else None, self.table,
                        ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.block_table, kv.page_size, n_q, n_kv, head_dim,
-                       self.rot_dim, write_kv)
+                       self.rot_dim, write_kv, v_head_dim=v_head_dim)
         return q
 
 
