@@ -427,6 +427,31 @@ def dofipel_config(width: int, heads: int, kv_heads: int, head_dim: int, ff: int
             "layers": layers}
 
 
+def ganupel_config(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab: int, n_layers: int,
+                   window: int) -> dict:
+    """A Ganupel configuration with a Llama shape's layer sizes. Layers cycle through four kinds: the two mixers
+    side by side (sigmoid-weight attention over a window, and a gated linear recurrence with as many heads, half
+    a head size of gate channels and a head size of value channels) + dense feed-forward, the same + routed experts,
+    a recurrent unit as wide as the model (one block per head) + routed experts, the two mixers + routed experts.
+    The routed feed-forward's active width (4 of 16 experts of ff / 4, beside 4 outputs that return the input)
+    is at most the dense one's."""
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+            "rot": {"base": 10000.0, "dims": head_dim}, "mask": {"size": window} if window else None}
+    right = {"heads": heads, "dim": head_dim // 2, "vdim": head_dim}
+    both = {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}
+    unit = {"width": width, "blocks": heads, "conv": 4}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": 16, "identity": 4, "top": 4, "scale": 1.0}, "expert": {"ff": ff // 4}}
+    layers = []
+    for i in range(n_layers):
+        kind = i % 4
+        if kind == 2:
+            layers.append({"type": "rglru", "mixer": dict(unit), "mlp": moe})
+        else:
+            layers.append({"type": "parallel", "mixer": json.loads(json.dumps(both)), "mlp": dense if kind == 0 else moe})
+    return {"architecture": "Ganupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers}
+
+
 def step_tables(engine, pk: dict, title: str, batch: int = 8) -> str:
     """Per-kernel tables (eager steps, CUDA events) of a decode step at `batch` sequences and of a 2,048-token
     prompt."""
@@ -465,7 +490,8 @@ def step_tables(engine, pk: dict, title: str, batch: int = 8) -> str:
 
 
 def run_designs(args, pk: dict, which: str = "Zemivik") -> str:
-    """Zemivik (or, with which="Dofipel", Dofipel with a window of 1,024) beside Llama at equal layer sizes (random weights, bfloat16): decode throughput at batch 1, 8 and 64
+    """Zemivik (or, with which="Dofipel", Dofipel with a window of 1,024) beside Llama at equal layer sizes, or, with
+    which="Ganupel", Ganupel beside Dofipel (random weights, bfloat16): decode throughput at batch 1, 8 and 64
     after 512-token prompts (captured steps, device time), prefill throughput of one 2,048-token prompt, and the
     per-kernel tables of both. Zemivik once without a mask (the attention work of Llama's) and once with a window
     of 1,024 tokens that keeps the first four. The shared vocabulary is kept small so that the layers, not the
@@ -477,7 +503,7 @@ def run_designs(args, pk: dict, which: str = "Zemivik") -> str:
     vocab = 32000
     shapes = [("1B layer sizes", CONFIG_1B), ("8B layer sizes", CONFIG_8B)]
     steps = min(args.steps, 64)
-    lines = [f"{which} beside Llama at equal layer sizes, {n_layers} layers, vocabulary {vocab}, bfloat16, random weights "
+    lines = [f"{which} beside {'Dofipel' if which == 'Ganupel' else 'Llama'} at equal layer sizes, {n_layers} layers, vocabulary {vocab}, bfloat16, random weights "
              f"(peaks: {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s, {pk['source']}).", "",
              "| layer sizes | design | decode b1 tok/s | ms/step | decode b8 tok/s | ms/step | decode b64 tok/s | ms/step | "
              f"prefill {PREFILL_TOKENS} tok/s | ms |", "|---|---|---|---|---|---|---|---|---|---|"]
@@ -493,6 +519,9 @@ def run_designs(args, pk: dict, which: str = "Zemivik") -> str:
         if which == "Dofipel":
             designs = [("Llama", llama),
                        ("Dofipel, window 1024", dofipel_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024))]
+        if which == "Ganupel":
+            designs = [("Dofipel, window 1024", dofipel_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024)),
+                       ("Ganupel, window 1024", ganupel_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024))]
         for design, cfg in designs:
             folder = scratch_folder("llmie_bench_design_")
             write_random_model(cfg, folder, seed=3, std=0.02)
@@ -614,8 +643,8 @@ def run_ours(args):
             with open(args.per_kernel_out, "w", encoding="utf-8") as f:
                 f.write(text + "\n")
         return 0
-    if args.designs or args.dofipel:
-        text = run_designs(args, pk, "Dofipel" if args.dofipel else "Zemivik")
+    if args.designs or args.dofipel or args.ganupel:
+        text = run_designs(args, pk, "Ganupel" if args.ganupel else "Dofipel" if args.dofipel else "Zemivik")
         print(text)
         if args.per_kernel_out:
             with open(args.per_kernel_out, "w", encoding="utf-8") as f:
@@ -790,6 +819,9 @@ def main():
     ap.add_argument("--dofipel", action="store_true",
                     help="the same comparison for Dofipel (windowed and latent attention, gated and routed "
                          "feed-forwards) beside Llama")
+    ap.add_argument("--ganupel", action="store_true",
+                    help="the same comparison for Ganupel (sigmoid-weight attention beside a gated linear recurrence, "
+                         "recurrent units, PolyNorm and routed feed-forwards) beside Dofipel, the closest design")
     ap.add_argument("--heads", type=int, default=32, help="query heads of --attention-sweep")
     ap.add_argument("--kv-heads", type=int, default=8, help="KV heads of --attention-sweep")
     ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128], help="head size of --attention-sweep")

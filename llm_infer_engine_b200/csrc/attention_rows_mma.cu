@@ -3,6 +3,8 @@
 // range of the key rows (a latent that is key and value at once), prompts and one-token steps alike, and the options
 // that change single scores (a cap c tanh(s / c), a bias by distance from a per-head table, a sink whose score is a
 // number per head) besides scale and window. bfloat16 in and out, float32 scores, softmax and accumulators.
+// With `sig_bias` (a number per query head) there is no softmax: a visible key's weight is sigmoid(score + that number),
+// nothing is normalised over the keys, and the running maximum, the rescaling and the final division fall away.
 //
 // All query heads that share a key/value head work on the same keys, so the rows of the problem are the (token, head)
 // pairs of one key/value head of one sequence: row r = token * G + head-in-group. A block of eight warps takes 32
@@ -40,6 +42,7 @@ struct RowsArgs {
   int bias_len;
   const float* sink_vals;        // [n_q] or null
   int sink;
+  const float* sig_bias;         // [n_q] or null: sigmoid weights instead of a softmax
   int shared_rows;               // 1: the values are columns of the staged key rows (no second fetch)
 };
 
@@ -137,6 +140,7 @@ attention_rows_mma_kernel(const RowsArgs p) {
 #pragma unroll
     for (int i = 0; i < NTW; ++i) acc[mt][i][0] = acc[mt][i][1] = acc[mt][i][2] = acc[mt][i][3] = 0.f;
   const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+  const float sig_b = (p.sig_bias && r0 + sm_row < n_rows) ? p.sig_bias[hk * G + (r0 + sm_row) % G] : 0.f;
   const int s_mt = warp >> 2, s_nt = warp & 3;            // the score tile of this warp
   const int n_vt = p.hdv / 8;                             // tiles of value columns there are
 
@@ -200,20 +204,26 @@ attention_rows_mma_kernel(const RowsArgs p) {
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      float pr[4], sum = 0.f;
+      float pr[4], al = 1.f;
+      if (p.sig_bias) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        pr[e] = vis[e] ? __expf(sc[e] - m_use) : 0.f;
-        sum += pr[e];
+        for (int e = 0; e < 4; ++e) pr[e] = vis[e] ? 1.f / (1.f + __expf(-(sc[e] + sig_b))) : 0.f;
+      } else {
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          pr[e] = vis[e] ? __expf(sc[e] - m_use) : 0.f;
+          sum += pr[e];
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        al = __expf(m_run - m_use);                       // 0 while the row has seen no key
+        l_run = l_run * al + sum;
+        m_run = m_new;
       }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-      const float al = __expf(m_run - m_use);             // 0 while the row has seen no key
-      l_run = l_run * al + sum;
-      m_run = m_new;
       __nv_bfloat162* pw = reinterpret_cast<__nv_bfloat162*>(P + sm_row * 40 + sm_key0);
       pw[0] = __floats2bfloat162_rn(pr[0], pr[1]);
       pw[1] = __floats2bfloat162_rn(pr[2], pr[3]);
@@ -261,7 +271,9 @@ attention_rows_mma_kernel(const RowsArgs p) {
   if ((lane & 7) == 0) {
     const int r = r0 + sm_row;
     float f = 0.f;
-    if (r < n_rows) {
+    if (r < n_rows && p.sig_bias) {
+      f = 1.f;
+    } else if (r < n_rows) {
       float l = l_run, num = 1.f;
       if (p.sink) {
         const float sv = p.sink_vals ? p.sink_vals[hk * G + r % G] : 0.f;
@@ -314,13 +326,15 @@ extern "C" int llmie_attention_rows_mma_supported(int hd, int hdv, int page_size
 // q [T, n_q hd], out [T, n_q hdv], caches as in llmie_attention_paged_ex (v_cache rows v_ld apart; shared_rows != 0: the
 // values are the first hdv columns of the key rows themselves), all bfloat16. cu_q int32 [n_seqs + 1]: where each
 // sequence's tokens start; seq_start int32 [n_seqs]: tokens held before this step; max_q_len: upper bound of a
-// sequence's tokens in this step (sizes the grid).
+// sequence's tokens in this step (sizes the grid). sig_bias float32 [n_q] or null.
 extern "C" int llmie_attention_rows_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
                                         const int* cu_q, const int* seq_slot, const int* seq_start,
                                         const int* block_table, int max_pages, int page_size, int n_seqs, int max_q_len,
                                         int n_q, int n_kv, int hd, int hdv, int v_ld, int shared_rows, float scale,
                                         int window, float softcap, const float* dist_bias, int bias_len,
-                                        const float* sink_vals, int sink, cudaStream_t stream) {
+                                        const float* sink_vals, int sink, const float* sig_bias,
+                                        cudaStream_t stream) {
+  if (sig_bias && (sink || softcap > 0.f || dist_bias)) return LLMIE_ERR_BAD_ARG;
   if (n_seqs < 0 || max_q_len < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_pages <= 0 || window < 0 || softcap < 0.f)
     return LLMIE_ERR_BAD_ARG;
   if ((dist_bias && bias_len <= 0) || (sink_vals && !sink) || v_ld < hdv) return LLMIE_ERR_BAD_ARG;
@@ -332,7 +346,7 @@ extern "C" int llmie_attention_rows_mma(const void* q, const void* k_cache, cons
   if (row_blocks > 0x7fffffffLL || n_kv > 65535 || n_seqs > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
   RowsArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
              cu_q, seq_slot, seq_start, block_table, max_pages, page_size, n_q, n_kv, hd, hdv, v_ld, scale, window,
-             softcap, dist_bias, bias_len, sink_vals, sink ? 1 : 0, shared_rows ? 1 : 0};
+             softcap, dist_bias, bias_len, sink_vals, sink ? 1 : 0, sig_bias, shared_rows ? 1 : 0};
   const size_t smem = rows_smem_bytes(hd, hdv, shared_rows != 0);
   dim3 grid((unsigned)row_blocks, n_kv, n_seqs);
   const int ntw = (hdv / 8 + kRmWarps - 1) / kRmWarps;

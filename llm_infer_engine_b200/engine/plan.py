@@ -102,8 +102,10 @@ class KernelPlan:
         return False
 
     def _sigmoid_attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, options, gate) -> bool:
-        """Attention without a softmax (weights sigmoid(score + a number per head), not normalised)."""
-        return False
+        """Attention without a softmax (weights sigmoid(score + a number per head), not normalised): the tensor-core
+        kernel by rows for prompts and one-token steps of the bfloat16 engine; anything it does not take (float32, head
+        sizes that are no multiples of 16) is the plain kernel's."""
+        return self._attention_by_rows(ctx, q, kv, out, n_q, n_kv, head_dim, options, gate)
 
     def _attention_by_rows(self, ctx, q, kv, out, n_q, n_kv, head_dim, options, gate) -> bool:
         """The tensor-core kernel whose rows are the (token, head) pairs of a key/value head: prompts and one-token
@@ -114,7 +116,8 @@ class KernelPlan:
             return False
         ops.attention_rows_mma(q, kv.k, kv.v, out, ctx.cu_q, ctx.seq_slot, ctx.seq_start, kv.block_table, kv.page_size,
                                ctx.n_seqs, ctx.max_q_len, n_q, n_kv, head_dim, options.scale, options.window,
-                               options.softcap, options.distance_bias, options.sink_values, options.sink)
+                               options.softcap, options.distance_bias, options.sink_values, options.sink,
+                               options.sigmoid_bias)
         if gate is not None:
             ops.sigmoid_gate(out, gate)
         return True

@@ -1408,10 +1408,12 @@ def attention_rows_mma_supported(head_dim: int, v_head_dim: int, page_size: int,
 def attention_rows_mma(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, page_size: int, n_seqs: int,
                        max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                        softcap: float = 0.0, dist_bias: Optional[torch.Tensor] = None,
-                       sink_values: Optional[torch.Tensor] = None, sink: bool = False):
+                       sink_values: Optional[torch.Tensor] = None, sink: bool = False,
+                       sigmoid_bias: Optional[torch.Tensor] = None):
     """Attention on the tensor cores with the (token, head) pairs of a key/value head as rows (bfloat16): prompts and
     one-token steps, any head size that is a multiple of 16, a value size of its own, values that are columns of the
-    key rows (v_cache a view into k_cache), scale, window, cap, bias by distance and sink as in attention_paged."""
+    key rows (v_cache a view into k_cache), scale, window, cap, bias by distance, sink and sigmoid weights as in
+    attention_paged."""
     T = q.shape[0]
     hdv = v_cache.shape[-1]
     _need(q, "q", torch.bfloat16, (T, n_q * head_dim))
@@ -1436,14 +1438,18 @@ def attention_rows_mma(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, bloc
     if sink_values is not None:
         _need(sink_values, "sink_values", torch.float32, (n_q,))
         sink = True
+    if sigmoid_bias is not None:
+        _need(sigmoid_bias, "sigmoid_bias", torch.float32, (n_q,))
     _work(2 * _nbytes(q) + 1.0 * STEP_HINT["kv_total"] * n_kv * (head_dim + (0 if shared_rows else hdv)) * 2,
           2.0 * n_q * (head_dim + hdv) * STEP_HINT["pairs"])
     f = _fn("attention_rows_mma", "llmie_attention_rows_mma",
-            [_c_void_p] * 8 + [_c_int] * 10 + [_c_float, _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p])
+            [_c_void_p] * 8 + [_c_int] * 10 + [_c_float, _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
+                                               _c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(),
              seq_start.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n_seqs, max_q_len, n_q, n_kv,
              head_dim, hdv, int(v_ld), 1 if shared_rows else 0, float(scale), int(window), float(softcap or 0.0),
-             _ptr(dist_bias), bias_len, _ptr(sink_values), 1 if sink else 0, _stream()), "attention_rows_mma")
+             _ptr(dist_bias), bias_len, _ptr(sink_values), 1 if sink else 0, _ptr(sigmoid_bias), _stream()),
+           "attention_rows_mma")
     return out
 
 

@@ -160,6 +160,16 @@ def route(u, w, p, r):
     return chosen, picked / (picked.sum(-1, keepdim=True) + 1e-20) * r["scale"]
 
 
+def choice_margin(u, w, p, r):
+    """[n]: how far the last chosen output's choice score lies above the best one not chosen (infinite when every
+    output is chosen). A token whose margin is of the size of rounding may choose otherwise in lower precision."""
+    s = torch.softmax(u @ w[p + "router"].T, dim=-1) + w[p + "correction"]
+    if s.shape[1] <= r["top"]:
+        return torch.full((u.shape[0],), float("inf"), dtype=u.dtype)
+    best = torch.topk(s, r["top"] + 1, dim=-1).values
+    return best[:, -2] - best[:, -1]
+
+
 def moe(u, w, p, f):
     """Experts are W_down relu(W_up u)^2; the last `identity` outputs of the router stand for experts that return
     their input."""
@@ -177,8 +187,9 @@ def moe(u, w, p, f):
     return out
 
 
-def forward(w, cfg, tokens, layers_out=None):
-    """Logits [n, vocab] of one sequence. `layers_out`, a list, receives the stream after every layer."""
+def forward(w, cfg, tokens, layers_out=None, margins_out=None):
+    """Logits [n, vocab] of one sequence. `layers_out`, a list, receives the stream after every layer; `margins_out`,
+    a list, the routers' choice margins [n] of every layer that has a router."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     for i, layer in enumerate(cfg["layers"]):
@@ -195,6 +206,8 @@ def forward(w, cfg, tokens, layers_out=None):
         if f is not None:
             u = norm_around_one(x, w[p + "norm2"], eps)
             y = dense_ff(u, w, p + "mlp.", eps) if f["kind"] == "dense" else moe(u, w, p + "mlp.", f)
+            if margins_out is not None and f["kind"] != "dense":
+                margins_out.append(choice_margin(u, w, p + "mlp.", f["router"]))
             x = x + w[p + "ls2"] * y
         if layers_out is not None:
             layers_out.append(x.clone())

@@ -83,6 +83,8 @@ def folder_for(tag):
                 t = torch.randn(t.shape, generator=g) * 0.15
             elif name.endswith(".mlp.act"):
                 t = torch.tensor([0.9, -0.6, 0.4, 0.1])
+            elif name.endswith(".right.f.b"):
+                t = t - 1.5                                          # gates that lean on their lower bound
             elif name.endswith(".mix.lam"):
                 t = torch.rand(t.shape, generator=g) * 4 - 7         # long memories: a state that is lost shows
             elif name.endswith(".mix.o") and not name.endswith((".left.o", ".right.o")):
@@ -113,19 +115,38 @@ def bound(dtype, want):
     return (3e-5 if dtype == "float32" else 0.05) * max(1.0, float(want.abs().max()))
 
 
+CLOSE_CALL = 0.01          # a router's choice margin below this may fall the other way in bfloat16
+_close_calls = {}
+
+
 def oracle(tag, requests):
+    """The plain logits of every request. Beside them it notes, per request, the tokens at which some router of the
+    plain model chooses by a margin that bfloat16 rounding can turn (the comparison in bfloat16 holds those tokens
+    to the count of positions over the bound, not to the worst-case factor)."""
     w = plain_weights(tag)
-    return {rid: plain.forward(w, CFGS[tag], toks).float() for rid, toks in requests.items()}
+    out = {}
+    for rid, toks in requests.items():
+        margins = []
+        out[rid] = plain.forward(w, CFGS[tag], toks, margins_out=margins).float()
+        close = torch.zeros(len(toks), dtype=torch.bool)
+        for m in margins:
+            close |= m < CLOSE_CALL
+        _close_calls[(tag, rid)] = close
+    return out
 
 
-def compare(got, want, dtype, what):
+def compare(got, want, dtype, what, tag=None):
     for rid in want:
         assert got[rid].shape == want[rid].shape, (what, rid)
         diff = (got[rid] - want[rid]).abs().max(dim=1).values
         tol_ = bound(dtype, want[rid])
         over = int((diff > tol_).sum())
         allowed = 0 if dtype == "float32" else max(1, len(diff) // 25)
-        assert over <= allowed and float(diff.max()) <= (tol_ if dtype == "float32" else 3 * tol_), (
+        firm = diff
+        if dtype != "float32" and (tag, rid) in _close_calls:
+            firm = diff[~_close_calls[(tag, rid)][:len(diff)]]
+        worst = float(firm.max()) if len(firm) else 0.0
+        assert over <= allowed and worst <= (tol_ if dtype == "float32" else 3 * tol_), (
             f"{what}: request {rid}: {over} of {len(diff)} positions over the bound {tol_:.3e}, worst "
             f"{float(diff.max()):.3e}, first at token {int((diff > tol_).nonzero()[0])}")
 
@@ -414,7 +435,7 @@ def test_every_schedule_matches_plain(tag, dtype):
         plans[f"pieces of {chunk}"] = helpers.plan_chunked(some if chunk == 2 else requests, chunk)
     for name, steps in plans.items():
         got = helpers.run_plan_engine(engine, steps)
-        compare(got, {rid: want[rid] for rid in got}, dtype, f"{tag}/{dtype}/{name}")
+        compare(got, {rid: want[rid] for rid in got}, dtype, f"{tag}/{dtype}/{name}", tag)
         assert engine.cache.free_slots() == engine.cache.n_slots and engine.cache.free_pages() == engine.cache.n_pages
     if dtype == "bfloat16":
         from llm_infer_engine_b200.kernels import ops
@@ -488,7 +509,7 @@ def test_trace_run_program_and_other_sizes_at_once(tmp_path):
     peak = max(sum(len(v) for v in requests.values()), 64)
     for dtype in ("float32", "bfloat16"):
         got = helpers.run_plan_trace_run(folder_for(tag), dtype, steps, peak, CFGS[tag]["vocab"])
-        compare(got, want, dtype, f"trace_run/{dtype}")
+        compare(got, want, dtype, f"trace_run/{dtype}", tag)
 
 
 @pytest.mark.parametrize("dtype,gap", [("float32", 1e-4), ("bfloat16", 0.3)])
