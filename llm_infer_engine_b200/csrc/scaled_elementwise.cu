@@ -110,14 +110,18 @@ extern "C" int llmie_scaled_add_rmsnorm(float* h, const void* d1, int d1_dtype, 
   return LLMIE_OK;
 }
 
-// z, y [T, n] of `dtype`; coef float32 [4] = (a, b, c, e) on the device. n <= 12,288.
+// z, y [T, n] of `dtype`; coef float32 [4] = (a, b, c, e) on the device. n <= 51,200 (a row in shared memory).
 extern "C" int llmie_poly_norm(const void* z, const float* coef, float eps, void* y, int n_tokens, int n, int dtype,
                                cudaStream_t stream) {
   if (n_tokens < 0 || n <= 0 || !coef) return LLMIE_ERR_BAD_ARG;
-  if ((size_t)n * sizeof(float) > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if ((size_t)n * sizeof(float) > 200 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (n_tokens == 0) return LLMIE_OK;
   const dim3 grid(n_tokens), block(row_block(n));
   const size_t smem = (size_t)n * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaFuncSetAttribute(poly_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(poly_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
   if (dtype == LLMIE_F32)
     launch_k(poly_norm_kernel<float>, grid, block, smem, stream, (const float*)z, coef, eps, (float*)y, n);
   else if (dtype == LLMIE_BF16)

@@ -191,7 +191,7 @@ def test_scaled_add_and_norm_in_one_kernel(dtype, size, deltas):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("rows,n", [(1, 20), (5, 136), (40, 1000), (300, 64)])
+@pytest.mark.parametrize("rows,n", [(1, 20), (5, 136), (40, 1000), (300, 64), (3, 14000)])
 def test_dense_feed_forward_with_normalised_powers(dtype, rows, n):
     ff, w = build("feed_forward", "dense_mlp", {"hidden": 48, "intermediate": n, "bias": False,
                                                 "activation": "poly_norm", "norm_eps": 1e-5}, dtype, seed=n, std=0.3)
