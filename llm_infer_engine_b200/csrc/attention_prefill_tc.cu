@@ -112,11 +112,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 // them): softcap c > 0 turns a scaled score s into c * tanh(s / c); dist_bias (float32 [n_q, bias_len]) adds a number per
 // query head and distance (query position - key position; bias_len - 1 and more share the last entry) after the cap,
 // unscaled; sink_vals (float32 [n_q]) is the sink's score per head instead of 0.
+// sigmoid_bias (float32 [n_q]) is another kind of attention and has an instantiation of its own (SIGMOID): the weight
+// of a visible key is sigmoid(scaled score + sigmoid_bias[head]), not normalised over the keys. No running maximum, no
+// sum, nothing exchanged between a row's two threads, and the output is the accumulated P.V as it is; the mask, the
+// P operand and the tensor-core protocol are the softmax kernel's.
 struct ScoreOptions {
   float softcap;
   const float* dist_bias;
   int bias_len;
   const float* sink_vals;
+  const float* sigmoid_bias;
 };
 
 __device__ __forceinline__ float tanh_approx(float x) {
@@ -125,7 +130,7 @@ __device__ __forceinline__ float tanh_approx(float x) {
   return y;
 }
 
-template <int HD, bool SCORED>
+template <int HD, bool SCORED, bool SIGMOID>
 __global__ void __maxnreg__(SCORED && HD == 64 ? 96 : AttnCfg<HD>::kMaxRegs)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -318,6 +323,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int qpos = start + t0 + r;                     // absolute position of this query
     const int lo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
     const float sl2 = scale * 1.4426950408889634f;       // exp(x * scale) = exp2(x * scale * log2 e)
+    const float sig_b = SIGMOID ? so.sigmoid_bias[head] * 1.4426950408889634f : 0.f;
     constexpr int kCols = kKTile / 2;                    // key columns of a tile this thread handles
     constexpr int kOut = HD / 2;                         // output columns this thread keeps
     float o[kOut];
@@ -373,6 +379,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int lo_rel = lo - kbase;
 #pragma unroll
       for (int c0 = 0; c0 < kCols; c0 += 32) {
+        if (SIGMOID && !edge) continue;           // nothing to mark, and no maximum is wanted
         uint32_t v[32];
         tmem_ld_32x32(lane_addr + b * 128 + half * kCols + c0, v);
         tmem_ld_wait();
@@ -395,6 +402,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
           }
           tmem_st_32x32(lane_addr + b * 128 + half * kCols + c0, v);
+        } else if (SIGMOID) {
+          // no maximum is wanted: only what this row may not see is marked, in the tiles where there is any
+          const unsigned span = (unsigned)(qpos - lo);
+          const int kept_rel = min(keep_first, qpos + 1) - kbase;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((unsigned)(c0 + i - lo_rel) > span && c0 + i >= kept_rel) v[i] = 0xff800000u;
+          tmem_st_32x32(lane_addr + b * 128 + half * kCols + c0, v);
         } else if (edge) {
           // A tile that the causal line or the window's far end crosses: the scores this row may not see become
           // -inf here, in tensor memory too, so that the second pass is the same for every tile (2^-inf = 0).
@@ -415,16 +430,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       if (edge || SCORED) tmem_st_wait();
       float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      float other;
-      if (!__all_sync(0xffffffffu, exchange(m_tile, other))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
-      m_tile = fmaxf(m_tile, other);
-      const float m_new = fmaxf(m_run, m_tile);
+      if (!SIGMOID) {
+        float other;
+        if (!__all_sync(0xffffffffu, exchange(m_tile, other))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
+        m_tile = fmaxf(m_tile, other);
+      }
+      const float m_new = SIGMOID ? 0.f : fmaxf(m_run, m_tile);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen no key yet
-      const float alpha = exp2_approx((m_run - m_use) * sl2);      // 0 while m_run is -inf
+      const float alpha = SIGMOID ? 1.f : exp2_approx((m_run - m_use) * sl2);      // 0 while m_run is -inf
       const float m_scaled = m_use * sl2;
       // pass 2: probabilities, their sum, and P in bfloat16 into the swizzled operand tile
       uint64_t ls[2] = {0ull, 0ull};             // four running sums, as two pairs
-      const uint64_t sl2_pair = pair_of(sl2, sl2), m_pair = pair_of(-m_scaled, -m_scaled);
+      // sigmoid(x) = 1 / (1 + 2^(-x log2 e)): the pairs then hold -scale log2 e and -bias log2 e
+      const uint64_t sl2_pair = SIGMOID ? pair_of(-sl2, -sl2) : pair_of(sl2, sl2);
+      const uint64_t m_pair = SIGMOID ? pair_of(-sig_b, -sig_b) : pair_of(-m_scaled, -m_scaled);
       // 32 keys from column c0 of this thread's half: probabilities, summed and packed two to a word
       auto probabilities = [&](int c0, uint32_t (&w)[16]) {
         uint32_t v[32];
@@ -437,9 +456,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           fma_pair(x0, x1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), sl2_pair, m_pair);
           p[i] = exp2_approx(x0);
           p[i + 1] = exp2_approx(x1);
+          if (SIGMOID) {                       // a key that is not seen: 2^(+inf), and 1 / inf = 0
+            p[i] = __fdividef(1.f, 1.f + p[i]);
+            p[i + 1] = __fdividef(1.f, 1.f + p[i + 1]);
+          }
         }
+        if (!SIGMOID) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) ls[(i >> 1) & 1] = add_pair(ls[(i >> 1) & 1], p[i], p[i + 1]);
+          for (int i = 0; i < 32; i += 2) ls[(i >> 1) & 1] = add_pair(ls[(i >> 1) & 1], p[i], p[i + 1]);
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) w[i] = pack_bf16(p[2 * i], p[2 * i + 1]);
       };
@@ -480,7 +505,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       else { LLMIE_FAIL(kStatusTimeoutMma); ok = false; }
     }
     // the row's sum is the two halves' sums (both were kept relative to the same running maximum)
-    if (ok) {
+    if (ok && !SIGMOID) {
       float other;
       if (exchange(l_run, other)) l_run += other;
       else { LLMIE_FAIL(kStatusTimeoutMma); ok = false; }
@@ -488,11 +513,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok && r < rows_here) {
       // the sink: one more term exp(0 - max) in the denominator (it has no value, the numerator stays);
       // a maximum far below zero makes the term infinite and the output zero, which is the limit
-      if (sink) {
+      if (sink && !SIGMOID) {
         const float sv = (SCORED && so.sink_vals) ? so.sink_vals[head] * 1.4426950408889634f : 0.f;
         l_run += exp2_approx(sv - m_run * sl2);
       }
-      const float inv = 1.f / l_run;
+      const float inv = SIGMOID ? 1.f : 1.f / l_run;
       const size_t row_off = ((size_t)(q_begin + t0 + r) * n_q + head) * HD + half * kOut;
       __nv_bfloat16* dst = out + row_off;
       const __nv_bfloat16* gr = gate ? gate + (size_t)(q_begin + t0 + r) * gate_ld + head * HD + half * kOut : nullptr;
@@ -520,7 +545,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
 }
 
-template <int HD, bool SCORED>
+template <int HD, bool SCORED, bool SIGMOID = false>
 static int launch_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q,
                           const int* seq_slot, const int* seq_start, const int* block_table, int max_pages,
                           int n_pages_total, int n_tokens, int n_seqs, int max_q_len, int n_q, int n_kv, float scale,
@@ -535,11 +560,11 @@ static int launch_prefill(const void* q, const void* k_cache, const void* v_cach
   if (rc != LLMIE_OK) return rc;
   rc = tc::make_tmap_bf16_2d(&map_v, v_cache, kv_rows, HD, HD, 64);
   if (rc != LLMIE_OK) return rc;
-  cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, SCORED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, SCORED, SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::kSmem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_q, (max_q_len + kQTile - 1) / kQTile, n_seqs);
-  attention_prefill_tc_kernel<HD, SCORED><<<grid, kAttnThreads, Cfg::kSmem, stream>>>(
+  attention_prefill_tc_kernel<HD, SCORED, SIGMOID><<<grid, kAttnThreads, Cfg::kSmem, stream>>>(
       map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total - 1,
       n_q, n_kv, scale, window, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld, status, so);
   LLMIE_LAUNCH_CHECK();
@@ -571,6 +596,7 @@ static int prefill_tc_entry(const void* q, const void* k_cache, const void* v_ca
   if (keep_first < 0 || (gate && (gate_ld < n_q * hd || gate_ld % 8 || !aligned16(gate)))) return LLMIE_ERR_BAD_ARG;
   if (!(scale > 0.f)) return LLMIE_ERR_BAD_ARG;   // the running maximum is taken before the scores are scaled
   if (so.softcap < 0.f || (so.dist_bias && so.bias_len <= 0) || (so.sink_vals && !sink)) return LLMIE_ERR_BAD_ARG;
+  if (so.sigmoid_bias && (so.softcap > 0.f || so.dist_bias || so.sink_vals || sink)) return LLMIE_ERR_BAD_ARG;
   if (!aligned16(q) || !aligned16(out) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
   if (n_tokens == 0 || n_seqs == 0 || max_q_len <= 0) return LLMIE_OK;
   if (n_seqs > 65535 || n_q > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
@@ -578,6 +604,8 @@ static int prefill_tc_entry(const void* q, const void* k_cache, const void* v_ca
 #define LLMIE_PREFILL_ARGS                                                                                            \
   q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total, n_tokens, n_seqs,       \
       max_q_len, n_q, n_kv, scale, window, keep_first, sink, gate, gate_ld, status, so, stream
+  if (so.sigmoid_bias && hd == 64) return launch_prefill<64, false, true>(LLMIE_PREFILL_ARGS);
+  if (so.sigmoid_bias && hd == 128) return launch_prefill<128, false, true>(LLMIE_PREFILL_ARGS);
   if (hd == 64) return scored ? launch_prefill<64, true>(LLMIE_PREFILL_ARGS) : launch_prefill<64, false>(LLMIE_PREFILL_ARGS);
   if (hd == 128) return scored ? launch_prefill<128, true>(LLMIE_PREFILL_ARGS) : launch_prefill<128, false>(LLMIE_PREFILL_ARGS);
 #undef LLMIE_PREFILL_ARGS
@@ -592,7 +620,7 @@ extern "C" int llmie_attention_prefill_tc(const void* q, const void* k_cache, co
                                           cudaStream_t stream) {
   return prefill_tc_entry(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total,
                           n_tokens, n_seqs, max_q_len, n_q, n_kv, hd, scale, window, keep_first, sink, gate, gate_ld,
-                          status, ScoreOptions{0.f, nullptr, 0, nullptr}, stream);
+                          status, ScoreOptions{0.f, nullptr, 0, nullptr, nullptr}, stream);
 }
 
 // The same with the options that change single scores (see ScoreOptions): a cap, a bias by distance, the sink's score
@@ -606,5 +634,20 @@ extern "C" int llmie_attention_prefill_tc_scored(const void* q, const void* k_ca
                                                  const float* sink_vals, cudaStream_t stream) {
   return prefill_tc_entry(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total,
                           n_tokens, n_seqs, max_q_len, n_q, n_kv, hd, scale, window, keep_first, sink, gate, gate_ld,
-                          status, ScoreOptions{softcap, dist_bias, bias_len, sink_vals}, stream);
+                          status, ScoreOptions{softcap, dist_bias, bias_len, sink_vals, nullptr}, stream);
+}
+
+// Attention without a softmax: the weight of a visible key is sigmoid(scaled score + sigmoid_bias[head]) (float32
+// [n_q]), not normalised over the keys; window, kept first keys and gate as above.
+extern "C" int llmie_attention_prefill_tc_sigmoid(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                                  const int* cu_q, const int* seq_slot, const int* seq_start,
+                                                  const int* block_table, int max_pages, int n_pages_total,
+                                                  int n_tokens, int n_seqs, int max_q_len, int n_q, int n_kv, int hd,
+                                                  float scale, int window, int keep_first, const void* gate,
+                                                  int gate_ld, int* status, const float* sigmoid_bias,
+                                                  cudaStream_t stream) {
+  if (!sigmoid_bias) return LLMIE_ERR_BAD_ARG;
+  return prefill_tc_entry(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total,
+                          n_tokens, n_seqs, max_q_len, n_q, n_kv, hd, scale, window, keep_first, 0, gate, gate_ld,
+                          status, ScoreOptions{0.f, nullptr, 0, nullptr, sigmoid_bias}, stream);
 }

@@ -9,10 +9,18 @@
 //
 //   matrix_gates       q = silu(q_raw), f = l + (1 - l) sigmoid(f_raw + b)           element-wise, float32 out
 //   matrix_scan        S <- diag(f_t) S + (1 - f_t) v_t^T ; o_t = S^T q_t            S [dim, vdim] per head
+//   matrix_scan_chunked  the same for long pieces, cut into chunks that run side by side (below)
 //   head_rmsnorm       o / sqrt(mean(o^2) + eps) * w over each head's vdim
 //   causal_conv        u_t = b + sum_j taps[:, K-1-j] x_(t-j), x before the step from the state's last K-1 inputs
 //   unit_gate_values   a = exp(-c r softplus(lam)), drive = sqrt(1 - a^2) i u, r and i sigmoids of given pre-activations
 //   unit_scan          S <- a_t S + drive_t ; out_t = S act(y_raw + b) ; the new conv state
+//   unit_scan_chunked  the same for long pieces, 32 chunks of a sequence side by side in one block
+//
+// Long pieces. Both recurrences are linear in the state, S_end = A S_start + B with A the product of the chunk's gates
+// and B what the chunk makes from a zero state. So a piece is cut into chunks; every chunk is run from zero (A and B),
+// the chunks' true starting states follow from a short chain over the chunks, and every chunk is run again from its
+// start, now with outputs. Twice the arithmetic, all of it float32 and in token order within a chunk; what differs
+// from the token-by-token order is the rounding of the chain's steps only.
 #include "common.cuh"
 #include <math.h>
 
@@ -48,26 +56,41 @@ constexpr int kScanR = 16;          // state rows a thread keeps at most
 // grid (column tiles, heads, sequences). A thread owns column j of its head's state and the rows [s R, (s+1) R) of it,
 // S = slices (a power of two up to 32, lanes that differ in their low bits), R = ceil(dim / S) <= kScanR. The next
 // token's gate, query and value are requested before the current token's products.
-template <typename T>
+// MODE 0: a sequence's whole piece, from the slot's state to the slot's state. MODE 1 and 2 work on chunk c =
+// blockIdx.z % NC of sequence blockIdx.z / NC, L tokens each, with ws float32 [n_seqs, NC, H, D, Dv] and decay float32
+// [n_seqs, NC, H, D]: MODE 1 runs a chunk that is not the sequence's last from a zero state, without outputs, and leaves
+// its end state in ws[c + 1] and the product of its gates in decay[c + 1]; MODE 2 runs a chunk from ws[c] with outputs,
+// and the last one writes the slot's state.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(kScanThreads)
 matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, const T* __restrict__ v, int v_ld,
                    float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
-                   float* __restrict__ o, int H, int D, int Dv, int S, int R, int write_state) {
+                   float* __restrict__ o, int H, int D, int Dv, int S, int R, int write_state,
+                   float* __restrict__ ws, float* __restrict__ decay, int L, int NC) {
   pdl_launch_dependents();
   pdl_wait();
   const int s = threadIdx.x & (S - 1);
   const int col = threadIdx.x / S;
   const int j = blockIdx.x * (kScanThreads / S) + col;
-  const int h = blockIdx.y, seq = blockIdx.z;
+  const int h = blockIdx.y;
+  const int seq = MODE == 0 ? blockIdx.z : blockIdx.z / NC;
+  const int chunk = MODE == 0 ? 0 : blockIdx.z - seq * NC;
   const bool live = j < Dv;
   const int jj = live ? j : Dv - 1;
   const int i0 = s * R;
-  const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+  const int seq_end = cu_q[seq + 1];
+  const int t0 = MODE == 0 ? cu_q[seq] : cu_q[seq] + chunk * L;
+  const int t1 = MODE == 0 ? seq_end : min(t0 + L, seq_end);
+  if (MODE == 1 && t1 >= seq_end) return;          // the last chunk (or none at all): nobody needs its end state
+  if (MODE == 2 && t0 >= seq_end) return;
   const int slot = seq_slot[seq];
   float* st = state + (((size_t)slot * H + h) * D) * Dv + jj;
+  const size_t HDDv = (size_t)H * D * Dv;
+  const float* start = MODE == 2 ? ws + ((size_t)seq * NC + chunk) * HDDv + ((size_t)h * D) * Dv + jj : st;
   float St[kScanR];
 #pragma unroll
-  for (int r = 0; r < kScanR; ++r) St[r] = (r < R && i0 + r < D) ? st[(size_t)(i0 + r) * Dv] : 0.f;
+  for (int r = 0; r < kScanR; ++r)
+    St[r] = (MODE != 1 && r < R && i0 + r < D) ? start[(size_t)(i0 + r) * Dv] : 0.f;
   float f[kScanR], q[kScanR], vj = 0.f;
   const size_t HD = (size_t)H * D;
   auto fetch = [&](int t) {
@@ -77,30 +100,72 @@ matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, c
     for (int r = 0; r < kScanR; ++r) {
       const bool ok = r < R && i0 + r < D;
       f[r] = ok ? fr[r] : 0.f;
-      q[r] = ok ? qr[r] : 0.f;
+      if (MODE != 1) q[r] = ok ? qr[r] : 0.f;
     }
     vj = to_f32(v[(size_t)t * v_ld + (size_t)h * Dv + jj]);
   };
+  float prod[kScanR];                               // MODE 1: the product of the chunk's gates
+#pragma unroll
+  for (int r = 0; r < kScanR; ++r) prod[r] = 1.f;
   if (t0 < t1) fetch(t0);
   for (int t = t0; t < t1; ++t) {
     float cf[kScanR], cq[kScanR];
     const float cv = vj;
 #pragma unroll
-    for (int r = 0; r < kScanR; ++r) { cf[r] = f[r]; cq[r] = q[r]; }
+    for (int r = 0; r < kScanR; ++r) { cf[r] = f[r]; cq[r] = MODE != 1 ? q[r] : 0.f; }
     if (t + 1 < t1) fetch(t + 1);
     float acc = 0.f;
 #pragma unroll
     for (int r = 0; r < kScanR; ++r) {
       St[r] = fmaf(cf[r], St[r], (1.f - cf[r]) * cv);
-      acc = fmaf(St[r], cq[r], acc);
+      if (MODE == 1) prod[r] *= cf[r];
+      else acc = fmaf(St[r], cq[r], acc);
     }
-    for (int off = 1; off < S; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (s == 0 && live) o[(size_t)t * H * Dv + (size_t)h * Dv + j] = acc;
+    if (MODE != 1) {
+      for (int off = 1; off < S; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      if (s == 0 && live) o[(size_t)t * H * Dv + (size_t)h * Dv + j] = acc;
+    }
   }
-  if (write_state && live) {
+  if (MODE == 1) {
+    float* end = ws + ((size_t)seq * NC + chunk + 1) * HDDv + ((size_t)h * D) * Dv + jj;
+    float* dec = decay + (((size_t)seq * NC + chunk + 1) * H + h) * D;
+#pragma unroll
+    for (int r = 0; r < kScanR; ++r)
+      if (r < R && i0 + r < D) {
+        if (live) end[(size_t)(i0 + r) * Dv] = St[r];
+        if (blockIdx.x == 0 && col == 0) dec[i0 + r] = prod[r];
+      }
+    return;
+  }
+  if (write_state && live && t1 >= seq_end) {
 #pragma unroll
     for (int r = 0; r < kScanR; ++r)
       if (r < R && i0 + r < D) st[(size_t)(i0 + r) * Dv] = St[r];
+  }
+}
+
+// The chain over a sequence's chunks, a thread per element of the state: ws[0] = the slot's state and
+// ws[c] = decay[c] (.) ws[c - 1] + ws[c] for the chunks the sequence has, so that ws[c] is where chunk c starts.
+__global__ void matrix_scan_chain_kernel(const float* __restrict__ state, const int* __restrict__ cu_q,
+                                         const int* __restrict__ seq_slot, float* __restrict__ ws,
+                                         const float* __restrict__ decay, int H, int D, int Dv, int L, int NC) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.y;
+  const size_t HDDv = (size_t)H * D * Dv;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= HDDv) return;
+  const int n = cu_q[seq + 1] - cu_q[seq];
+  const int nc = (n + L - 1) / L;
+  if (nc <= 0) return;
+  const size_t hi = e / Dv;                         // (head, row) of the element
+  float S = state[(size_t)seq_slot[seq] * HDDv + e];
+  float* w = ws + (size_t)seq * NC * HDDv + e;
+  const float* d = decay + (size_t)seq * NC * H * D + hi;
+  w[0] = S;
+  for (int c = 1; c < nc; ++c) {
+    S = fmaf(d[(size_t)c * H * D], S, w[(size_t)c * HDDv]);
+    w[(size_t)c * HDDv] = S;
   }
 }
 
@@ -234,6 +299,108 @@ __global__ void unit_scan_kernel(const float* __restrict__ gates, const T* __res
     if (k < K - 1) cs[(size_t)k * C] = keep[k];
 }
 
+// The same recurrence for long pieces: a block is 32 channels by kUnitChunks chunks of one sequence. Every thread runs
+// its chunk from zero (the product of its a's and what it makes), the first warp chains the chunks' starting states in
+// shared memory, and every thread runs its chunk again from its start, now with outputs.
+constexpr int kUnitChunks = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kUnitChunks)
+unit_scan_chunked_kernel(const float* __restrict__ gates, const T* __restrict__ proj, int ld, int y_off, int x_off,
+                         const float* __restrict__ y_bias, const float* __restrict__ x_bias, int act,
+                         float* __restrict__ state, float* __restrict__ conv_state, const int* __restrict__ cu_q,
+                         const int* __restrict__ seq_slot, T* __restrict__ out, int C, int bw, int K, int write_state) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float sA[kUnitChunks][33], sB[kUnitChunks][33];
+  const int cx = threadIdx.x, ky = threadIdx.y;
+  const int c = blockIdx.x * 32 + cx;
+  const int seq = blockIdx.y;
+  const bool live = c < C;
+  const int cc = live ? c : C - 1;
+  const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+  const int n = t1 - t0;
+  const int L = (n + kUnitChunks - 1) / kUnitChunks;
+  const int a0 = min(t0 + ky * L, t1), a1 = min(a0 + L, t1);
+  const int slot = seq_slot[seq];
+  const int g = cc / bw, e = cc - g * bw;
+  const float* gr = gates + (size_t)g * 2 * bw + e;
+  constexpr int U = 4;
+  {
+    float A = 1.f, B = 0.f;
+    int t = a0;
+    for (; t + U <= a1; t += U) {
+      float a[U], d[U];
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        a[k] = gr[(size_t)(t + k) * 2 * C];
+        d[k] = gr[(size_t)(t + k) * 2 * C + bw];
+      }
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        A *= a[k];
+        B = fmaf(a[k], B, d[k]);
+      }
+    }
+    for (; t < a1; ++t) {
+      const float a = gr[(size_t)t * 2 * C];
+      A *= a;
+      B = fmaf(a, B, gr[(size_t)t * 2 * C + bw]);
+    }
+    sA[ky][cx] = A;
+    sB[ky][cx] = B;
+  }
+  __syncthreads();
+  if (ky == 0) {                                       // sB[k] becomes where chunk k starts
+    float S = state[(size_t)slot * C + cc];
+    for (int k = 0; k < kUnitChunks; ++k) {
+      const float next = fmaf(sA[k][cx], S, sB[k][cx]);
+      sB[k][cx] = S;
+      S = next;
+    }
+    if (write_state && live) state[(size_t)slot * C + c] = S;
+  }
+  __syncthreads();
+  if (live) {
+    const float yb = y_bias ? y_bias[c] : 0.f;
+    float S = sB[ky][cx];
+    int t = a0;
+    for (; t + U <= a1; t += U) {
+      float a[U], d[U], y[U];
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        a[k] = gr[(size_t)(t + k) * 2 * C];
+        d[k] = gr[(size_t)(t + k) * 2 * C + bw];
+        y[k] = apply_act(to_f32(proj[(size_t)(t + k) * ld + y_off + c]) + yb, act);
+      }
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        S = fmaf(a[k], S, d[k]);
+        out[(size_t)(t + k) * C + c] = from_f32<T>(S * y[k]);
+      }
+    }
+    for (; t < a1; ++t) {
+      S = fmaf(gr[(size_t)t * 2 * C], S, gr[(size_t)t * 2 * C + bw]);
+      out[(size_t)t * C + c] = from_f32<T>(S * apply_act(to_f32(proj[(size_t)t * ld + y_off + c]) + yb, act));
+    }
+  }
+  if (!write_state || !live || ky != 0) return;
+  // the last K-1 inputs of the sequence: this step's, and before them what the state held
+  float* cs = conv_state + (size_t)slot * (K - 1) * C + c;
+  const float xb = x_bias ? x_bias[c] : 0.f;
+  float keep[kMaxTaps];
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) {
+    if (k < K - 1) {
+      const int m = n - (K - 1) + k;                  // place within the step, negative = before it
+      keep[k] = m >= 0 ? to_f32(proj[(size_t)(t0 + m) * ld + x_off + c]) + xb : cs[(size_t)(K - 1 + m) * C];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k)
+    if (k < K - 1) cs[(size_t)k * C] = keep[k];
+}
+
 }  // namespace llmie
 
 using namespace llmie;
@@ -279,11 +446,53 @@ extern "C" int llmie_matrix_scan(const float* qa, const float* fg, const void* v
   const dim3 grid((Dv + cols - 1) / cols, H, n_seqs), block(kScanThreads);
   if (grid.y > 65535 || grid.z > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (dtype == LLMIE_F32)
-    launch_k(matrix_scan_kernel<float>, grid, block, 0, stream, qa, fg, (const float*)v, v_ld, state, cu_q, seq_slot, o,
-             H, D, Dv, S, R, write_state);
+    launch_k(matrix_scan_kernel<float, 0>, grid, block, 0, stream, qa, fg, (const float*)v, v_ld, state, cu_q, seq_slot,
+             o, H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1);
   else if (dtype == LLMIE_BF16)
-    launch_k(matrix_scan_kernel<__nv_bfloat16>, grid, block, 0, stream, qa, fg, (const __nv_bfloat16*)v, v_ld, state,
-             cu_q, seq_slot, o, H, D, Dv, S, R, write_state);
+    launch_k(matrix_scan_kernel<__nv_bfloat16, 0>, grid, block, 0, stream, qa, fg, (const __nv_bfloat16*)v, v_ld, state,
+             cu_q, seq_slot, o, H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+template <typename T>
+static void matrix_scan_chunked_launch(const float* qa, const float* fg, const T* v, int v_ld, float* state,
+                                       const int* cu_q, const int* seq_slot, float* o, float* ws, float* decay,
+                                       int n_seqs, int H, int D, int Dv, int S, int R, int L, int NC, int write_state,
+                                       cudaStream_t stream) {
+  const int cols = kScanThreads / S;
+  const dim3 grid((Dv + cols - 1) / cols, H, n_seqs * NC), block(kScanThreads);
+  launch_k(matrix_scan_kernel<T, 1>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
+           write_state, ws, decay, L, NC);
+  const size_t HDDv = (size_t)H * D * Dv;
+  launch_k(matrix_scan_chain_kernel, dim3((unsigned)((HDDv + 255) / 256), n_seqs), dim3(256), 0, stream,
+           (const float*)state, cu_q, seq_slot, ws, (const float*)decay, H, D, Dv, L, NC);
+  launch_k(matrix_scan_kernel<T, 2>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
+           write_state, ws, decay, L, NC);
+}
+
+// llmie_matrix_scan for long pieces: chunks of `chunk` tokens run side by side. n_chunks >= ceil(longest piece / chunk);
+// ws float32 [n_seqs, n_chunks, H, D, Dv] and decay float32 [n_seqs, n_chunks, H, D] are scratch.
+extern "C" int llmie_matrix_scan_chunked(const float* qa, const float* fg, const void* v, int v_ld, float* state,
+                                         const int* cu_q, const int* seq_slot, float* o, float* ws, float* decay,
+                                         int n_seqs, int H, int D, int Dv, int chunk, int n_chunks, int write_state,
+                                         int dtype, cudaStream_t stream) {
+  if (n_seqs < 0 || H <= 0 || D <= 0 || Dv <= 0 || v_ld < H * Dv || chunk <= 0 || n_chunks <= 0 || !ws || !decay)
+    return LLMIE_ERR_BAD_ARG;
+  if (D > 32 * kScanR) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (n_seqs == 0) return LLMIE_OK;
+  int S = 1;
+  while (S * kScanR < D) S <<= 1;
+  const int R = (D + S - 1) / S;
+  if (H > 65535 || (long long)n_seqs * n_chunks > 65535 || n_seqs > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (dtype == LLMIE_F32)
+    matrix_scan_chunked_launch(qa, fg, (const float*)v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D, Dv, S,
+                               R, chunk, n_chunks, write_state, stream);
+  else if (dtype == LLMIE_BF16)
+    matrix_scan_chunked_launch(qa, fg, (const __nv_bfloat16*)v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D,
+                               Dv, S, R, chunk, n_chunks, write_state, stream);
   else
     return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
@@ -350,16 +559,31 @@ extern "C" int llmie_unit_gate_values(float* gates, const float* u, const float*
 
 // gates as left by llmie_unit_gate_values; proj [T, ld] of `dtype` with the output gate's raw projection at y_off and
 // the convolution's input at x_off; state float32 [slots, C]; conv_state float32 [slots, K-1, C]; out [T, C] of `dtype`.
+// chunked != 0: the form for long pieces (every sequence's piece in 32 chunks side by side).
 extern "C" int llmie_unit_scan(const float* gates, const void* proj, int ld, int y_off, int x_off, const float* y_bias,
                                const float* x_bias, int act, float* state, float* conv_state, const int* cu_q,
                                const int* seq_slot, void* out, int n_seqs, int C, int bw, int K, int write_state,
-                               int dtype, cudaStream_t stream) {
+                               int chunked, int dtype, cudaStream_t stream) {
   if (n_seqs < 0 || C <= 0 || bw <= 0 || C % bw || K <= 0 || y_off < 0 || x_off < 0 || ld < y_off + C || ld < x_off + C)
     return LLMIE_ERR_BAD_ARG;
   if (act < 0 || act > 4) return LLMIE_ERR_BAD_ARG;
   if (K > kMaxTaps) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (n_seqs == 0) return LLMIE_OK;
   if (n_seqs > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (chunked) {
+    const dim3 grid((C + 31) / 32, n_seqs), block(32, kUnitChunks);
+    if (dtype == LLMIE_F32)
+      launch_k(unit_scan_chunked_kernel<float>, grid, block, 0, stream, gates, (const float*)proj, ld, y_off, x_off,
+               y_bias, x_bias, act, state, conv_state, cu_q, seq_slot, (float*)out, C, bw, K, write_state);
+    else if (dtype == LLMIE_BF16)
+      launch_k(unit_scan_chunked_kernel<__nv_bfloat16>, grid, block, 0, stream, gates, (const __nv_bfloat16*)proj, ld,
+               y_off, x_off, y_bias, x_bias, act, state, conv_state, cu_q, seq_slot, (__nv_bfloat16*)out, C, bw, K,
+               write_state);
+    else
+      return LLMIE_ERR_DTYPE;
+    LLMIE_LAUNCH_CHECK();
+    return LLMIE_OK;
+  }
   const int threads = C >= 128 ? 128 : ((C + 31) / 32) * 32;
   const dim3 grid((C + threads - 1) / threads, n_seqs), block(threads);
   if (dtype == LLMIE_F32)

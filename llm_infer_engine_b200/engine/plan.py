@@ -11,6 +11,8 @@ from ..kernels import ops
 
 class KernelPlan:
     MIN_COUNTERS = 4096            # counters allocated at least; more than any one-token step of 64 lanes needs
+    SIGMOID_TC_FROM = 17           # sigmoid-weight attention: pieces this long go to the tcgen05 kernel (tiles of 128
+                                   # query rows of ONE head), shorter ones to the kernel whose rows are (token, head) pairs
 
     def __init__(self, engine):
         self.engine = engine
@@ -102,9 +104,19 @@ class KernelPlan:
         return False
 
     def _sigmoid_attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, options, gate) -> bool:
-        """Attention without a softmax (weights sigmoid(score + a number per head), not normalised): the tensor-core
-        kernel by rows for prompts and one-token steps of the bfloat16 engine; anything it does not take (float32, head
-        sizes that are no multiples of 16) is the plain kernel's."""
+        """Attention without a softmax (weights sigmoid(score + a number per head), not normalised). Prompts of the
+        bfloat16 engine with head size 64 or 128 (values of the same size): the tcgen05 kernel. Other prompts and the
+        one-token steps: the tensor-core kernel by rows. What that does not take (float32, head sizes that are no
+        multiples of 16) is the plain kernel's."""
+        if not ctx.decode and ctx.max_q_len >= self.SIGMOID_TC_FROM and options.scale > 0 \
+                and kv.v.shape[-1] == head_dim and kv.v.is_contiguous() \
+                and ops.attention_prefill_tc_supported(head_dim, kv.page_size, q.dtype) \
+                and (gate is None or not (gate.stride(0) % 8 or gate.data_ptr() % 16)):
+            ops.attention_prefill_tc(q, kv.k, kv.v, out, ctx.cu_q, ctx.seq_slot, ctx.seq_start, kv.block_table,
+                                     kv.page_size, ctx.n_seqs, ctx.max_q_len, n_q, n_kv, head_dim, options.scale,
+                                     options.window, options.keep_first, False, gate,
+                                     sigmoid_bias=options.sigmoid_bias)
+            return True
         return self._attention_by_rows(ctx, q, kv, out, n_q, n_kv, head_dim, options, gate)
 
     def _attention_by_rows(self, ctx, q, kv, out, n_q, n_kv, head_dim, options, gate) -> bool:

@@ -889,12 +889,14 @@ def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, bl
                          n_seqs: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
                          window: int = 0, keep_first: int = 0, sink: bool = False,
                          gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                         dist_bias: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None):
+                         dist_bias: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None,
+                         sigmoid_bias: Optional[torch.Tensor] = None):
     """Causal attention for runs of new tokens on the tcgen05 tensor cores, K and V read from the
     paged cache by TMA. q, out bfloat16 [T, n_q hd] with sequences packed (cu_q int32 [n + 1]);
     seq_start int32 [n]: tokens each sequence held before this step. The caches' last page must be
     a scratch page. head_dim 64 or 128, pages of 64. keep_first, sink and gate as in attention_paged (the gate's
-    rows must start on 16 bytes)."""
+    rows must start on 16 bytes). With sigmoid_bias (float32 [n_q]) there is no softmax: the weight of a visible key is
+    sigmoid(scaled score + sigmoid_bias[head]), not normalised (no sink, cap or bias by distance with it)."""
     T = q.shape[0]
     gate_ld = _row_slice(gate, "gate", torch.bfloat16, T, n_q * head_dim) if gate is not None else 0
     if gate is not None and (gate_ld % 8 or gate.data_ptr() % 16):
@@ -912,6 +914,19 @@ def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, bl
     if not scale > 0:
         raise KernelError(f"attention_prefill_tc: the scale must be positive, got {scale}")
     _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
+    if sigmoid_bias is not None:
+        if softcap or dist_bias is not None or sink_values is not None or sink:
+            raise KernelError("attention_prefill_tc: sigmoid weights take no sink, cap or bias by distance")
+        _need(sigmoid_bias, "sigmoid_bias", torch.float32, (n_q,))
+        f = _fn("attention_prefill_tc", "llmie_attention_prefill_tc_sigmoid",
+                [_c_void_p] * 8 + [_c_int] * 8 + [_c_float, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                                  _c_void_p])
+        _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_q.data_ptr(),
+                 seq_slot.data_ptr(), seq_start.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                 k_cache.shape[0], T, n_seqs, max_q_len, n_q, n_kv, head_dim, float(scale), int(window),
+                 int(keep_first), _ptr(gate), gate_ld, tc_status_word(q.device).data_ptr(), sigmoid_bias.data_ptr(),
+                 _stream()), "attention_prefill_tc_sigmoid")
+        return out
     if softcap or dist_bias is not None or sink_values is not None:
         # the options that change single scores: a cap, a bias by distance [n_q, L], the sink's score per head
         bias_len = 0
@@ -1517,12 +1532,25 @@ def matrix_gates(proj, q_off: int, f_off: int, f_bias, lower, q_out, f_out):
              q_out.data_ptr(), f_out.data_ptr(), T, n, _dt(proj, "proj"), _stream()), "matrix_gates")
 
 
+# Long pieces of the recurrences run as chunks side by side. Which arithmetic a sequence gets depends on its own piece
+# alone, never on what else is in the step: the matrix scan cuts every piece at multiples of SCAN_CHUNK tokens and a
+# piece of one chunk goes through the very operations of the unchunked kernel; the unit scan cuts a piece into
+# UNIT_CHUNKS equal chunks and a piece of up to UNIT_CHUNKS tokens does the same. So the chunked kernels are launched
+# whenever the step's longest piece has more than one chunk. (Only a step whose chunks' starting states would pass
+# SCAN_SCRATCH_BYTES gets longer chunks.)
+SCAN_CHUNK = 64
+UNIT_CHUNKS = 32
+SCAN_SCRATCH_BYTES = 1 << 30
+
+
 def matrix_scan(q, f, v, state, cu_q, seq_slot, out, n_seqs: int, heads: int, dim: int, vdim: int,
-                write_state: bool = True):
+                write_state: bool = True, max_len: int = 0):
     """Per sequence and head, from the state S [dim, vdim] the slot holds: S <- diag(f_t) S + (1 - f_t) v_t^T and
     out_t = S^T q_t for each of the step's tokens in order; the new S is written back. q, f float32 [T, heads dim];
     v [T, heads vdim] (possibly a column slice) float32 or bfloat16; state float32 [slots, heads, dim, vdim];
-    out float32 [T, heads vdim]."""
+    out float32 [T, heads vdim]. `max_len`: an upper bound of the longest piece, if the caller knows one; long pieces
+    are cut into chunks that run side by side (each chunk from zero, a chain over the chunks' ends, each chunk again
+    from its true start), which changes rounding only."""
     T = q.shape[0]
     _need(q, "q", torch.float32, (T, heads * dim))
     _need(f, "f", torch.float32, (T, heads * dim))
@@ -1533,6 +1561,21 @@ def matrix_scan(q, f, v, state, cu_q, seq_slot, out, n_seqs: int, heads: int, di
     v_ld = _row_slice(v, "v", v.dtype, T, heads * vdim)
     _work(_nbytes(q, f, out) + T * heads * vdim * v.element_size() + 2.0 * n_seqs * heads * dim * vdim * 4,
           4.0 * T * heads * dim * vdim)
+    if max_len > SCAN_CHUNK and n_seqs > 0:
+        chunk, per_chunk = SCAN_CHUNK, n_seqs * heads * dim * vdim * 4
+        while -(-max_len // chunk) * per_chunk > SCAN_SCRATCH_BYTES and chunk < max_len:
+            chunk *= 2
+        n_chunks = -(-max_len // chunk)
+        if 2 <= n_chunks and n_seqs * n_chunks <= 65535:
+            ws = torch.empty((n_seqs, n_chunks, heads, dim, vdim), dtype=torch.float32, device=q.device)
+            decay = torch.empty((n_seqs, n_chunks, heads, dim), dtype=torch.float32, device=q.device)
+            _work(3.0 * _nbytes(ws) + _nbytes(f) + T * heads * vdim * v.element_size(), 4.0 * T * heads * dim * vdim)
+            f_ = _fn("recurrent", "llmie_matrix_scan_chunked",
+                     [_c_void_p, _c_void_p, _c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 8 + [_c_void_p])
+            _check(f_(q.data_ptr(), f.data_ptr(), v.data_ptr(), v_ld, state.data_ptr(), cu_q.data_ptr(),
+                      seq_slot.data_ptr(), out.data_ptr(), ws.data_ptr(), decay.data_ptr(), n_seqs, heads, dim, vdim,
+                      chunk, n_chunks, 1 if write_state else 0, _dt(v, "v"), _stream()), "matrix_scan_chunked")
+            return out
     f_ = _fn("recurrent", "llmie_matrix_scan", [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                                                 _c_void_p] + [_c_int] * 6 + [_c_void_p])
     _check(f_(q.data_ptr(), f.data_ptr(), v.data_ptr(), v_ld, state.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(),
@@ -1595,11 +1638,12 @@ def unit_gate_values(gates, u, r_bias, i_bias, lam, c_decay: float, block_width:
 
 
 def unit_scan(gates, proj, y_off: int, x_off: int, y_bias, x_bias, act: int, state, conv_state, cu_q, seq_slot, out,
-              n_seqs: int, block_width: int, write_state: bool = True):
+              n_seqs: int, block_width: int, write_state: bool = True, max_len: int = 0):
     """Per sequence and channel, from the slot's state S: S <- a_t S + drive_t, out_t = S * act(proj[t, y_off + c] +
     y_bias[c]) for the step's tokens in order (gates as `unit_gate_values` leaves them); the new S and the last K-1
     inputs of the convolution (proj[:, x_off + c] + x_bias) are written back. state float32 [slots, C]; conv_state
-    float32 [slots, K-1, C]; out [T, C] of proj's dtype."""
+    float32 [slots, K-1, C]; out [T, C] of proj's dtype. `max_len`: an upper bound of the longest piece, if the caller
+    knows one; long pieces run as 32 chunks side by side, which changes rounding only."""
     T, C = out.shape
     K = conv_state.shape[1] + 1
     _need(gates, "gates", torch.float32, (T, 2 * C))
@@ -1614,9 +1658,10 @@ def unit_scan(gates, proj, y_off: int, x_off: int, y_bias, x_bias, act: int, sta
     _need(seq_slot, "seq_slot", torch.int32)
     _work(_nbytes(gates, out) + T * C * proj.element_size())
     f = _fn("recurrent", "llmie_unit_scan", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
-                                             _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p] + [_c_int] * 6 +
+                                             _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p] + [_c_int] * 7 +
             [_c_void_p])
     _check(f(gates.data_ptr(), proj.data_ptr(), proj.shape[1], int(y_off), int(x_off), _ptr(y_bias), _ptr(x_bias),
              int(act), state.data_ptr(), conv_state.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(), out.data_ptr(),
-             n_seqs, C, int(block_width), K, 1 if write_state else 0, _dt(proj, "proj"), _stream()), "unit_scan")
+             n_seqs, C, int(block_width), K, 1 if write_state else 0, 1 if max_len > UNIT_CHUNKS else 0,
+             _dt(proj, "proj"), _stream()), "unit_scan")
     return out

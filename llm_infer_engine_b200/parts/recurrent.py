@@ -90,7 +90,7 @@ class GatedLinearRecurrence(Mixer):
         ops.matrix_gates(proj, 0, self.nq, self.f_bias, self.lower, q, f)
         read = torch.empty((T, self.nv), dtype=torch.float32, device=dev)
         ops.matrix_scan(q, f, proj[:, 2 * self.nq:], unit.state["S"], ctx.cu_q, ctx.seq_slot, read, ctx.n_seqs,
-                        self.n_heads, self.dim, self.v_dim, write_state=owns_cache)
+                        self.n_heads, self.dim, self.v_dim, write_state=owns_cache, max_len=ctx.max_q_len)
         normed = torch.empty((T, self.nv), dtype=proj.dtype, device=dev)
         ops.head_rmsnorm(read, self.norm_w, self.eps, normed, self.v_dim)
         trace.pop()
@@ -176,7 +176,7 @@ class GatedRecurrentUnit(Mixer):
         ops.unit_gate_values(gates, u, self.ra_bias, self.ri_bias, self.lam, self.decay, bw)
         out = torch.empty((T, C), dtype=proj.dtype, device=dev)
         ops.unit_scan(gates, proj, 0, C, self.y_bias, self.x_bias, self.activation, state, conv_state, ctx.cu_q,
-                      ctx.seq_slot, out, ctx.n_seqs, bw, write_state=owns_cache)
+                      ctx.seq_slot, out, ctx.n_seqs, bw, write_state=owns_cache, max_len=ctx.max_q_len)
         trace.pop()
         trace.push("Output_proj")
         y = self.o(out, out_dtype=torch.float32)

@@ -266,6 +266,44 @@ def test_matrix_scan_in_pieces_equals_the_plain_loop(heads, dim, vdim):
     assert float((state[2] - 7.0).abs().max()) == 0.0 and float(state[0].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 20, 24), (3, 64, 64), (1, 130, 40), (2, 48, 136)])
+def test_matrix_scan_of_long_pieces_in_chunks(heads, dim, vdim):
+    """Pieces long enough for the form that runs chunks side by side: three sequences of unequal lengths (one of them
+    a single chunk, one ending exactly at a chunk's end), states handed from piece to piece and to single tokens; some
+    gates sit next to 0 and next to 1, where a product of gates over a chunk is smallest and a state lives longest."""
+    from llm_infer_engine_b200.kernels import ops
+    g = torch.Generator().manual_seed(dim + vdim)
+    lens = [701, 322, 135]
+    q = [torch.randn(n, heads, dim, generator=g) for n in lens]
+    f = [torch.rand(n, heads, dim, generator=g) for n in lens]
+    for x in f:
+        x[:, :, 0::5] = 1 - x[:, :, 0::5] ** 4 * 0.01              # remembers for hundreds of tokens
+        x[:, :, 1::7] = x[:, :, 1::7] ** 4 * 0.01                   # forgets at once
+    v = [torch.randn(n, heads, vdim, generator=g) for n in lens]
+    want = []
+    for i in range(3):
+        S = torch.zeros(heads, dim, vdim, dtype=torch.float64)
+        rows = []
+        for t in range(lens[i]):
+            ft = f[i][t].double()
+            S = ft[:, :, None] * S + (1 - ft)[:, :, None] * v[i][t].double()[:, None, :]
+            rows.append(torch.einsum("hdv,hd->hv", S, q[i][t].double()).reshape(-1))
+        want.append(torch.stack(rows))
+    state = torch.zeros(5, heads, dim, vdim, device=DEV)
+    state[2] = 7.0
+    slots = torch.tensor([3, 1, 4], dtype=torch.int32, device=DEV)
+    held = [0, 0, 0]
+    for pieces in ([300, 192, 5], [1, 1, 1], [400, 129, 129]):
+        cu = torch.tensor([0, pieces[0], pieces[0] + pieces[1], sum(pieces)], dtype=torch.int32, device=DEV)
+        cat = lambda xs: torch.cat([xs[i][held[i]:held[i] + pieces[i]].reshape(pieces[i], -1) for i in range(3)]).to(DEV)
+        out = torch.empty(sum(pieces), heads * vdim, device=DEV)
+        ops.matrix_scan(cat(q), cat(f), cat(v), state, cu, slots, out, 3, heads, dim, vdim, max_len=max(pieces))
+        ref = torch.cat([want[i][held[i]:held[i] + pieces[i]] for i in range(3)])
+        assert float((out.cpu().double() - ref).abs().max()) <= 2e-5 * max(1.0, float(ref.abs().max())), pieces
+        held = [h + p for h, p in zip(held, pieces)]
+    assert float((state[2] - 7.0).abs().max()) == 0.0 and float(state[0].abs().max()) == 0.0
+
+
 # ------------------------------------------------------------------------------------------ parts alone
 def _run_mixer_in_pieces(mixer, cache, dtype, xs, want, schedule, unit_scope=None):
     slots = [cache.take_slot() for _ in xs]
@@ -350,6 +388,30 @@ def test_recurrent_unit_in_pieces(dtype, width, blocks, taps):
     _run_mixer_in_pieces(mixer, cache, dtype, xs2, [plain.gated_recurrent_unit(xs2[0].double(), wd, "", m)], ([3], [27]))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,blocks,taps", [(64, 4, 4), (100, 5, 3), (40, 1, 1)])
+def test_recurrent_unit_over_long_pieces(dtype, width, blocks, taps):
+    """Pieces long enough for the form that runs a sequence's chunks side by side, beside short ones in the same step,
+    then single tokens and a second long piece that starts from the state the first one left."""
+    from llm_infer_engine_b200.cache import Cache
+    hidden = 56
+    mixer, w = build("mixer", "gated_recurrent_unit", {"hidden": hidden, "width": width, "blocks": blocks, "taps": taps,
+                                                       "decay": 8.0}, dtype, seed=width + 1, std=0.25)
+    g = torch.Generator().manual_seed(width - taps)
+    for name in ("y.b", "x.b", "conv.b", "ra.b", "ri.b"):
+        w[name] = (torch.randn(w[name].shape, generator=g) * 0.3).to(torch.bfloat16).float()
+    w["conv"] = (torch.randn(width, taps, generator=g) * 0.5).to(torch.bfloat16).float()
+    w["lam"] = (torch.rand(width, generator=g) * 9 - 9).to(torch.bfloat16).float()      # some channels keep for long
+    mixer.load({k: v.to(DEV, DTYPES[dtype]) for k, v in w.items()})
+    wd = {k: v.double() for k, v in w.items()}
+    m = {"width": width, "blocks": blocks, "conv": taps}
+    cache = Cache([mixer.cache_requests()], 4, 64 * 24, 1024, DTYPES[dtype], DEV)
+    cache.take_slot()
+    xs = [torch.randn(n, hidden, generator=g).to(DTYPES[dtype]) for n in (520, 180, 40)]
+    want = [plain.gated_recurrent_unit(x.double(), wd, "", m) for x in xs]
+    _run_mixer_in_pieces(mixer, cache, dtype, xs, want, ([257, 130, 3], [1, 1, 1], [262, 49, 36]))
+
+
 # ------------------------------------------------------------------------------------------ the attention's edges
 def _edge_case(dtype, hd, hdv, n_q, n_kv, window, n, q_len, probe):
     """A sequence of n keys of which the last q_len are this step's queries; the LAST query points straight at key
@@ -404,7 +466,7 @@ EDGES = [  # window, keys, probe, may the last query (position keys - 1) see it
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [(24, 40, 4, 2), (64, 64, 6, 1), (128, 128, 2, 2), (32, 16, 6, 3)])
-@pytest.mark.parametrize("q_len", [1, 2, 37])
+@pytest.mark.parametrize("q_len", [1, 2, 37, 200])
 def test_keys_at_every_edge_stand_out(dtype, shape, q_len):
     """A probe key that the query may see puts the marker into the output (about 50); one that it may not see leaves
     the output small. Plain kernel (float32, odd sizes) and the tensor-core kernels (bfloat16)."""
