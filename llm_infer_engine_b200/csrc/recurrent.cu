@@ -189,32 +189,55 @@ __global__ void head_rmsnorm_kernel(const float* __restrict__ o, const float* __
 // ------------------------------------------------------------------------------------------ vector state
 constexpr int kMaxTaps = 16;
 
-// a thread per (token, channel). x = proj[:, x_off + c] + x_bias; inputs before the step come from conv_state
-// [slots, K-1, C] (the last K-1 inputs of the sequence so far, zeros at its start).
+// A thread is a channel over a run of `tile` consecutive packed tokens. x = proj[:, x_off + c] + x_bias; inputs before
+// the step come from conv_state [slots, K-1, C] (the last K-1 inputs of the sequence so far, zeros at its start). The
+// thread keeps the last K inputs in registers: a token that follows its predecessor in the same sequence loads ONE new
+// input, the first token of a run or of a sequence's piece loads all K. Oldest input first: a fixed order of summation.
 template <typename T>
 __global__ void causal_conv_kernel(const T* __restrict__ proj, int ld, int x_off, const float* __restrict__ x_bias,
                                    const float* __restrict__ taps, const float* __restrict__ conv_bias,
                                    const float* __restrict__ conv_state, const int* __restrict__ cu_q,
                                    const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
-                                   float* __restrict__ u, int C, int K, size_t total) {
+                                   float* __restrict__ u, int C, int K, int n_tokens, int tile) {
   pdl_launch_dependents();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float tp[kMaxTaps], w[kMaxTaps];
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) tp[k] = k < K ? taps[(size_t)c * K + k] : 0.f;       // weights: no kernel writes them
+  const float xb = x_bias ? x_bias[c] : 0.f;
+  const float cb = conv_bias ? conv_bias[c] : 0.f;
   pdl_wait();
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (; i < total; i += stride) {
-    const int t = (int)(i / C);
-    const int c = (int)(i - (size_t)t * C);
+  const int ta = blockIdx.y * tile, tb = min(ta + tile, n_tokens);
+  int prev_seq = -1;
+  for (int t = ta; t < tb; ++t) {
     const int seq = tok_seq[t];
     const int p = t - cu_q[seq];                      // place within this step's piece of the sequence
-    const float* old = conv_state + (size_t)seq_slot[seq] * (K - 1) * C + c;
-    const float xb = x_bias ? x_bias[c] : 0.f;
-    float acc = conv_bias ? conv_bias[c] : 0.f;
-    for (int j = K - 1; j >= 0; --j) {                // oldest input first: a fixed order of summation
-      const int m = p - j;
-      const float x = m >= 0 ? to_f32(proj[(size_t)(t - j) * ld + x_off + c]) + xb : old[(size_t)(K - 1 + m) * C];
-      acc = fmaf(taps[(size_t)c * K + (K - 1 - j)], x, acc);
+    if (seq != prev_seq || p == 0) {
+      const float* old = conv_state + (size_t)seq_slot[seq] * (K - 1) * C + c;
+#pragma unroll
+      for (int k = 0; k < kMaxTaps; ++k) {
+        if (k < K) {
+          const int m = p - (K - 1 - k);              // w[k] is the input K-1-k tokens back
+          w[k] = m >= 0 ? to_f32(proj[(size_t)(t - (K - 1 - k)) * ld + x_off + c]) + xb
+                        : old[(size_t)(K - 1 + m) * C];
+        }
+      }
+      prev_seq = seq;
+    } else {
+#pragma unroll
+      for (int k = 0; k + 1 < kMaxTaps; ++k)
+        if (k + 1 < K) w[k] = w[k + 1];
+      const float x = to_f32(proj[(size_t)t * ld + x_off + c]) + xb;
+#pragma unroll
+      for (int k = 0; k < kMaxTaps; ++k)
+        if (k == K - 1) w[k] = x;
     }
-    u[i] = acc;
+    float acc = cb;
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k)
+      if (k < K) acc = fmaf(tp[k], w[k], acc);
+    u[(size_t)t * C + c] = acc;
   }
 }
 
@@ -529,14 +552,16 @@ extern "C" int llmie_causal_conv(const void* proj, int ld, int x_off, const floa
   if (n_tokens < 0 || C <= 0 || K <= 0 || x_off < 0 || ld < x_off + C) return LLMIE_ERR_BAD_ARG;
   if (K > kMaxTaps) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (n_tokens == 0) return LLMIE_OK;
-  const size_t total = (size_t)n_tokens * C;
-  const dim3 grid(sweep_blocks(total, 256)), block(256);
+  const int tile = n_tokens >= 1024 ? 16 : (n_tokens >= 64 ? 4 : 1);
+  const int threads = C >= 128 ? 128 : ((C + 31) / 32) * 32;
+  const dim3 grid((C + threads - 1) / threads, (n_tokens + tile - 1) / tile), block(threads);
+  if (grid.y > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (dtype == LLMIE_F32)
     launch_k(causal_conv_kernel<float>, grid, block, 0, stream, (const float*)proj, ld, x_off, x_bias, taps, conv_bias,
-             conv_state, cu_q, tok_seq, seq_slot, u, C, K, total);
+             conv_state, cu_q, tok_seq, seq_slot, u, C, K, n_tokens, tile);
   else if (dtype == LLMIE_BF16)
     launch_k(causal_conv_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)proj, ld, x_off, x_bias,
-             taps, conv_bias, conv_state, cu_q, tok_seq, seq_slot, u, C, K, total);
+             taps, conv_bias, conv_state, cu_q, tok_seq, seq_slot, u, C, K, n_tokens, tile);
   else
     return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
