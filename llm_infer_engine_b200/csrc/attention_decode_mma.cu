@@ -63,6 +63,9 @@ __device__ __forceinline__ unsigned md_pack(float a, float b) {
 // Three more change single scores: softcap c > 0 turns a scaled score s into c * tanh(s / c); dist_bias (float32
 // [n_q, bias_len]) adds a number per query head and distance (distances of bias_len - 1 and more share the last entry)
 // after the cap; sink_vals (float32 [n_q]) is the sink's score per head instead of 0.
+// sigmoid_bias (float32 [n_q]) is another kind of attention: the weight of a visible key is sigmoid(scaled score +
+// sigmoid_bias[head]) and nothing is normalised over the keys. The kernel then runs with every maximum fixed at 0 (all
+// its rescaling factors become 1), takes the weights as they are, and leaves the division by the sum out.
 struct MdOptions {
   int keep_first;
   int sink;
@@ -72,6 +75,7 @@ struct MdOptions {
   const float* dist_bias;
   int bias_len;
   const float* sink_vals;
+  const float* sigmoid_bias;
 };
 
 __device__ __forceinline__ float md_tanh(float x) {
@@ -101,7 +105,7 @@ __device__ __forceinline__ float md_gated(float v, const __nv_bfloat16* gate_row
 template <int HD>
 __device__ __forceinline__ void md_merge_head(const float* part_m, const float* part_l, const float* part_acc,
                                               __nv_bfloat16* out_row, size_t base, int r0, int r1, int extra, int sink,
-                                              const __nv_bfloat16* gate_row, float sv = 0.f) {
+                                              const __nv_bfloat16* gate_row, float sv = 0.f, bool unnormalised = false) {
   const int lane = threadIdx.x & 31;
   const int n = extra + r1 - r0 + 1;
   auto run_of = [&](int i) { return i < extra ? i : r0 + i - extra; };
@@ -132,7 +136,8 @@ __device__ __forceinline__ void md_merge_head(const float* part_m, const float* 
   denom = warp_sum(denom);
 #pragma unroll
   for (int k = 0; k < HD / 32; ++k)
-    out_row[lane + 32 * k] = __float2bfloat16_rn(md_gated(md_finish(num[k], denom, M, sink, sv), gate_row, lane + 32 * k));
+    out_row[lane + 32 * k] = __float2bfloat16_rn(
+        md_gated(unnormalised ? num[k] : md_finish(num[k], denom, M, sink, sv), gate_row, lane + 32 * k));
 }
 
 // grid (n_runs, n_kv * chunks, n_seqs), chunks = ceil(G / 16); WARPS warps per block.
@@ -275,6 +280,9 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
   // rows g and g + 8 of the query tile are query heads hk * G + g0 + g (+ 8); rows beyond the group read row 0's table
   const float* bias_lo = opt.dist_bias ? opt.dist_bias + (size_t)(hk * G + g0 + (g < ng ? g : 0)) * opt.bias_len : nullptr;
   const float* bias_hi = opt.dist_bias ? opt.dist_bias + (size_t)(hk * G + g0 + (g + 8 < ng ? g + 8 : 0)) * opt.bias_len : nullptr;
+  const bool sig = opt.sigmoid_bias != nullptr;
+  const float pb_lo = sig ? opt.sigmoid_bias[hk * G + g0 + (g < ng ? g : 0)] : 0.f;
+  const float pb_hi = sig ? opt.sigmoid_bias[hk * G + g0 + (g + 8 < ng ? g + 8 : 0)] : 0.f;
   // ldmatrix row addresses: lane i gives row (i & 7) of matrix (i >> 3)
   const int lm_r = lane & 7, lm_m = lane >> 3;
   for (int idx = 0; p <= p_last; ++idx) {
@@ -344,6 +352,14 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
       for (int c = 0; c < 2; ++c) {
         const int key = nt * 8 + 2 * t + c;
         const bool vis = (key >= first && key < last) || key < kept_here;
+        if (sig) {
+          // the weight itself, 1 / (1 + 2^(-(s + b) log2 e)); a key that is not seen weighs nothing
+          const float a = fmaf(s[nt][c], scale, pb_lo) * -1.4426950408889634f;
+          const float b = fmaf(s[nt][2 + c], scale, pb_hi) * -1.4426950408889634f;
+          s[nt][c] = vis ? __fdividef(1.f, 1.f + md_exp2(a)) : 0.f;
+          s[nt][2 + c] = vis ? __fdividef(1.f, 1.f + md_exp2(b)) : 0.f;
+          continue;
+        }
         if (scored) {
           // the cap and the bias by distance work on the scaled score itself; then into log2 units
           float a = s[nt][c] * scale, b = s[nt][2 + c] * scale;
@@ -366,6 +382,7 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
         mx_hi = fmaxf(mx_hi, s[nt][2 + c]);
       }
     }
+    if (sig) mx_lo = mx_hi = 0.f;                        // no maximum: every factor below becomes 1 (0 for the first unit)
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
@@ -379,8 +396,8 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
     unsigned pa[2][4];                                   // P as A fragments: 2 steps of 16 keys
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
-      const float p0 = md_exp2(s[nt][0] - n_lo), p1 = md_exp2(s[nt][1] - n_lo);
-      const float p2 = md_exp2(s[nt][2] - n_hi), p3 = md_exp2(s[nt][3] - n_hi);
+      const float p0 = sig ? s[nt][0] : md_exp2(s[nt][0] - n_lo), p1 = sig ? s[nt][1] : md_exp2(s[nt][1] - n_lo);
+      const float p2 = sig ? s[nt][2] : md_exp2(s[nt][2] - n_hi), p3 = sig ? s[nt][3] : md_exp2(s[nt][3] - n_hi);
       sum_lo += p0 + p1;
       sum_hi += p2 + p3;
       pa[nt >> 1][(nt & 1) * 2] = md_pack(p0, p1);
@@ -458,7 +475,7 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
     if (n_runs == 1) {
       const __nv_bfloat16* gate_row = opt.gate ? opt.gate + (size_t)seq * opt.gate_ld + ((size_t)hk * G + g0 + row) * HD : nullptr;
       const float sv = opt.sink_vals ? opt.sink_vals[(size_t)hk * G + g0 + row] * 1.4426950408889634f : 0.f;
-      out[head * HD + d] = __float2bfloat16_rn(md_gated(md_finish(num, den, M, opt.sink, sv), gate_row, d));
+      out[head * HD + d] = __float2bfloat16_rn(md_gated(sig ? num : md_finish(num, den, M, opt.sink, sv), gate_row, d));
     } else {
       part_acc[(head * n_runs + run) * HD + d] = num;
       if (d == 0) {
@@ -486,7 +503,8 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_ca
     const size_t head = (size_t)seq * n_q + (size_t)hk * G + g0 + row;
     const __nv_bfloat16* gate_row = opt.gate ? opt.gate + (size_t)seq * opt.gate_ld + ((size_t)hk * G + g0 + row) * HD : nullptr;
     const float sv = opt.sink_vals ? opt.sink_vals[(size_t)hk * G + g0 + row] * 1.4426950408889634f : 0.f;
-    md_merge_head<HD>(part_m, part_l, part_acc, out + head * HD, head * n_runs, r0, r1, extra, opt.sink, gate_row, sv);
+    md_merge_head<HD>(part_m, part_l, part_acc, out + head * HD, head * n_runs, r0, r1, extra, opt.sink, gate_row, sv,
+                      opt.sigmoid_bias != nullptr);
   }
 }
 
@@ -612,10 +630,10 @@ extern "C" int llmie_attention_decode_mma(const void* q, const void* k_cache, co
                                           cudaStream_t stream) {
   return decode_mma_entry(q, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen, block_table,
                           max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs, nullptr, 0,
-                          0, 0, MdOptions{0, 0, nullptr, 0, 0.f, nullptr, 0, nullptr}, stream);
+                          0, 0, MdOptions{0, 0, nullptr, 0, 0.f, nullptr, 0, nullptr, nullptr}, stream);
 }
 
-// The same with the options of MdOptions: kept first keys, a sink, an output gate.
+// The same with the options of MdOptions: kept first keys, a sink, an output gate, changed scores, sigmoid weights.
 extern "C" int llmie_attention_decode_mma_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
                                              float* part_m, float* part_l, float* part_acc, int* counters,
                                              const int* seq_slot, const int* seq_kvlen, const int* block_table,
@@ -623,12 +641,13 @@ extern "C" int llmie_attention_decode_mma_ex(const void* q, const void* k_cache,
                                              float scale, int window, int pages_per_run, int n_runs, int keep_first,
                                              int sink, const void* gate, int gate_ld, float softcap,
                                              const float* dist_bias, int bias_len, const float* sink_vals,
-                                             cudaStream_t stream) {
+                                             const float* sigmoid_bias, cudaStream_t stream) {
   if (softcap < 0.f || (dist_bias && bias_len <= 0) || (sink_vals && !sink)) return LLMIE_ERR_BAD_ARG;
+  if (sigmoid_bias && (sink || softcap > 0.f || dist_bias)) return LLMIE_ERR_BAD_ARG;
   return decode_mma_entry(q, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen, block_table,
                           max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs, nullptr, 0,
                           0, 0, MdOptions{keep_first, sink ? 1 : 0, (const __nv_bfloat16*)gate, gate_ld, softcap, dist_bias,
-                                          bias_len, sink_vals}, stream);
+                                          bias_len, sink_vals, sigmoid_bias}, stream);
 }
 
 // The same with position encoding and the cache write inside: qkv bfloat16 [n_seqs, (n_q + 2 n_kv) hd] holds the
@@ -647,5 +666,5 @@ extern "C" int llmie_attention_decode_mma_rope(const void* qkv, void* k_cache, v
   return decode_mma_entry(qkv, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen,
                           block_table, max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs,
                           reinterpret_cast<const float2*>(rope), table_len, (n_q + 2 * n_kv) * hd, write_kv ? 1 : 0,
-                          MdOptions{0, 0, nullptr, 0, 0.f, nullptr, 0, nullptr}, stream);
+                          MdOptions{0, 0, nullptr, 0, 0.f, nullptr, 0, nullptr, nullptr}, stream);
 }

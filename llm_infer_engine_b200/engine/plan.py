@@ -105,16 +105,26 @@ class KernelPlan:
 
     def _sigmoid_attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, options, gate) -> bool:
         """Attention without a softmax (weights sigmoid(score + a number per head), not normalised). Prompts of the
-        bfloat16 engine with head size 64 or 128 (values of the same size): the tcgen05 kernel. Other prompts and the
-        one-token steps: the tensor-core kernel by rows. What that does not take (float32, head sizes that are no
+        bfloat16 engine with head size 64 or 128 (values of the same size): the tcgen05 kernel; their one-token steps:
+        the kernel with a warp per cache page. Other sizes and short pieces: the tensor-core kernel by rows. What that does not take (float32, head sizes that are no
         multiples of 16) is the plain kernel's."""
-        if not ctx.decode and ctx.max_q_len >= self.SIGMOID_TC_FROM and options.scale > 0 \
-                and kv.v.shape[-1] == head_dim and kv.v.is_contiguous() \
-                and ops.attention_prefill_tc_supported(head_dim, kv.page_size, q.dtype) \
-                and (gate is None or not (gate.stride(0) % 8 or gate.data_ptr() % 16)):
+        square = kv.v.shape[-1] == head_dim and kv.v.is_contiguous()
+        aligned_gate = gate is None or not (gate.stride(0) % 8 or gate.data_ptr() % 16)
+        if not ctx.decode and ctx.max_q_len >= self.SIGMOID_TC_FROM and options.scale > 0 and square and aligned_gate \
+                and ops.attention_prefill_tc_supported(head_dim, kv.page_size, q.dtype):
             ops.attention_prefill_tc(q, kv.k, kv.v, out, ctx.cu_q, ctx.seq_slot, ctx.seq_start, kv.block_table,
                                      kv.page_size, ctx.n_seqs, ctx.max_q_len, n_q, n_kv, head_dim, options.scale,
                                      options.window, options.keep_first, False, gate,
+                                     sigmoid_bias=options.sigmoid_bias)
+            return True
+        if ctx.decode and self.decode_attention != "split" and square and aligned_gate \
+                and ops.attention_decode_mma_supported(head_dim, q.dtype, kv.page_size):
+            pages = ops.attention_decode_mma_pages(ctx.n_seqs, n_q, n_kv, ctx.max_kv_len)
+            n_runs = ((ctx.max_kv_len + 63) // 64 + pages - 1) // pages
+            counters = self._decode_counters(ops.decode_counter_ints(ctx.n_seqs, n_q, n_kv), q.device)
+            ops.attention_decode_mma(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, kv.page_size,
+                                     n_q, n_kv, head_dim, options.scale, options.window, pages, n_runs,
+                                     counters=counters, keep_first=options.keep_first, gate=gate,
                                      sigmoid_bias=options.sigmoid_bias)
             return True
         return self._attention_by_rows(ctx, q, kv, out, n_q, n_kv, head_dim, options, gate)

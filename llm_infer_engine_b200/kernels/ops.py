@@ -557,11 +557,12 @@ def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_ta
                          counters: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None,
                          keep_first: int = 0, sink: bool = False, gate: Optional[torch.Tensor] = None,
                          softcap: float = 0.0, dist_bias: Optional[torch.Tensor] = None,
-                         sink_values: Optional[torch.Tensor] = None):
+                         sink_values: Optional[torch.Tensor] = None, sigmoid_bias: Optional[torch.Tensor] = None):
     """Attention for a one-token step on the tensor cores (bfloat16): a warp per cache page, the warps of a
     block merged in shared memory. Arguments as attention_decode; n_runs * pages_per_run pages must cover
     the longest sequence. With n_runs == 1 neither scratch nor counters are touched. keep_first, sink and gate
-    as in attention_paged."""
+    as in attention_paged. With sigmoid_bias (float32 [n_q]) there is no softmax: the weight of a visible key is
+    sigmoid(scaled score + sigmoid_bias[head]), not normalised (no sink, cap or bias by distance with it)."""
     n = q.shape[0]
     gate_ld = _row_slice(gate, "gate", torch.bfloat16, n, n_q * head_dim) if gate is not None else 0
     _need(q, "q", torch.bfloat16, (n, n_q * head_dim))
@@ -588,7 +589,11 @@ def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_ta
     _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
     f = _fn("attention_decode_mma", "llmie_attention_decode_mma_ex",
             [_c_void_p] * 11 + [_c_int] * 6 + [_c_float] + [_c_int] * 5 + [_c_void_p, _c_int, _c_float, _c_void_p,
-                                                                            _c_int, _c_void_p, _c_void_p])
+                                                                            _c_int, _c_void_p, _c_void_p, _c_void_p])
+    if sigmoid_bias is not None:
+        if sink or softcap or dist_bias is not None or sink_values is not None:
+            raise KernelError("attention_decode_mma: sigmoid weights take no sink, cap or bias by distance")
+        _need(sigmoid_bias, "sigmoid_bias", torch.float32, (n_q,))
     bias_len = 0
     if dist_bias is not None:
         _need(dist_bias, "dist_bias", torch.float32, (n_q, None))
@@ -600,7 +605,8 @@ def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_ta
              (base + 4 * n_ml) or None, (base + 8 * n_ml) or None, cptr, seq_slot.data_ptr(), seq_kvlen.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], page_size, n, n_q, n_kv, head_dim, float(scale),
              int(window), int(pages_per_run), int(n_runs), int(keep_first), 1 if sink else 0, _ptr(gate), gate_ld,
-             float(softcap or 0.0), _ptr(dist_bias), bias_len, _ptr(sink_values), _stream()), "attention_decode_mma")
+             float(softcap or 0.0), _ptr(dist_bias), bias_len, _ptr(sink_values), _ptr(sigmoid_bias), _stream()),
+           "attention_decode_mma")
     return out
 
 
