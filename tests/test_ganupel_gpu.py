@@ -161,7 +161,7 @@ def tol(dtype, scale):
 
 # ------------------------------------------------------------------------------------------ kernels alone
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("size", [200, 204, 2048])
+@pytest.mark.parametrize("size", [200, 202, 204, 2048])
 @pytest.mark.parametrize("deltas", [(), ("float32",), ("bfloat16",), ("float32", "float32"), ("bfloat16", "float32")])
 def test_scaled_add_and_norm_in_one_kernel(dtype, size, deltas):
     """h += s (.) (c1 d1 + c2 d2) and the norm with a weight stored around zero; all rows, and selected rows alone."""
