@@ -5,7 +5,8 @@ from .llama import LlamaConfig, RopeScaling
 from .zemivik import ZemivikConfig
 from .dofipel import DofipelConfig
 from .ganupel import GanupelConfig
+from .burinex import BurinexConfig
 
 __all__ = ["Architecture", "ConfigError", "architecture_of", "known_architectures", "load_config",
            "read_config_json", "register_architecture", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec",
-           "LlamaConfig", "RopeScaling", "ZemivikConfig", "DofipelConfig", "GanupelConfig"]
+           "LlamaConfig", "RopeScaling", "ZemivikConfig", "DofipelConfig", "GanupelConfig", "BurinexConfig"]

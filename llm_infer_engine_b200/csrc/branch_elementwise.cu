@@ -124,6 +124,95 @@ __global__ void branch_norm_add_vec_kernel(float* __restrict__ h, const Y* __res
 }
 
 // ------------------------------------------------------------------------------------------
+// Norm AFTER the residual sum (post-norm), with a learned scale per channel on the branch:
+//   x = alpha * h[t] + s (.) y[t];  h[t] = x * rsqrt(mean(x^2) + eps) * w;  act[t] = h[t] rounded to A (optional)
+// s is optional (null = ones). The stream stays float32. One block per row.
+template <typename Y, typename A>
+__global__ void scaled_sum_norm_kernel(float* __restrict__ h, const Y* __restrict__ y, const float* __restrict__ s,
+                                       float alpha, const float* __restrict__ w, float eps, A* __restrict__ act,
+                                       int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row_buf[];
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const Y* yr = y + (size_t)t * d;
+  float* hr = h + (size_t)t * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float b = to_f32(yr[i]) * (s ? s[i] : 1.f);
+    const float x = fmaf(alpha, hr[i], b);
+    row_buf[i] = x;
+    ss += x * x;
+  }
+  ss = block_sum(ss, red);
+  const float rstd = 1.f / sqrtf(ss / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = row_buf[i] * rstd * w[i];
+    hr[i] = v;
+    if (act) act[(size_t)t * d + i] = from_f32<A>(v);
+  }
+}
+
+// The same for rows of at most 8 * 1024 elements with d % 8 == 0: a thread owns one run of 8 elements, kept in
+// registers between the two passes, with 16-byte loads and stores.
+template <typename Y, typename A>
+__global__ void scaled_sum_norm_vec_kernel(float* __restrict__ h, const Y* __restrict__ y,
+                                           const float* __restrict__ s, float alpha, const float* __restrict__ w,
+                                           float eps, A* __restrict__ act, int d) {
+  pdl_launch_dependents();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const int i = threadIdx.x * 8;
+  const bool active = i < d;
+  float x[8], sv[8], wv[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { x[e] = 0.f; sv[e] = 1.f; wv[e] = 0.f; }
+  if (active) {                      // weights: no kernel writes them
+    if (s) load8(s + i, sv);
+    load8(w + i, wv);
+  }
+  pdl_wait();
+  float* hr = h + (size_t)t * d + i;
+  if (active) {
+    float hv[8];
+    load8(y + (size_t)t * d + i, x);
+    load8(hr, hv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = fmaf(alpha, hv[e], x[e] * sv[e]);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+  ss = block_sum(ss, red);
+  const float rstd = 1.f / sqrtf(ss / (float)d + eps);
+  if (active) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = x[e] * rstd * wv[e];
+    store8(hr, x);
+    if (act) store8(act + (size_t)t * d + i, x);
+  }
+}
+
+// RMS norm of a run of columns of wider rows: out[t, i] = x * rsqrt(mean(x^2) + eps) * w[i], x = src[t * ld + off + i],
+// i < n (the latent that queries pass through). float32 arithmetic, one rounding at the store. One block per row.
+template <typename T>
+__global__ void rmsnorm_cols_kernel(const T* __restrict__ src, int ld, int off, const float* __restrict__ w, float eps,
+                                    T* __restrict__ out, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const T* xr = src + (size_t)t * ld + off;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) { const float x = to_f32(xr[i]); ss += x * x; }
+  ss = block_sum(ss, red);
+  const float rstd = 1.f / sqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    out[(size_t)t * n + i] = from_f32<T>(to_f32(xr[i]) * rstd * w[i]);
+}
+
+// ------------------------------------------------------------------------------------------
 // out[t, j] = act(u[t, j] + bias[j]); bias optional. Activations: 0 none, 1 relu, 2 relu squared, 3 gelu (tanh
 // form), 4 silu.
 template <typename T, typename O>
@@ -186,9 +275,11 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, A* __restrict__ ou
   for (; i < total; i += stride) out[i] = from_f32<A>(x[i]);
 }
 
-// out[t, j] *= sigmoid(gate[t * ld + j])
+// out[t, j] *= sigmoid(gate[t * ld + j / group]): group 1 = a gate per element, group = a head's value size = one
+// gate per head
 template <typename T>
-__global__ void sigmoid_gate_kernel(T* __restrict__ out, const T* __restrict__ gate, int ld, int n, size_t total) {
+__global__ void sigmoid_gate_kernel(T* __restrict__ out, const T* __restrict__ gate, int ld, int n, int group,
+                                    size_t total) {
   pdl_launch_dependents();
   pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -196,13 +287,19 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ out, const T* __restrict__ g
   for (; i < total; i += stride) {
     const size_t t = i / n;
     const int j = (int)(i - t * n);
-    const float g = to_f32(gate[t * ld + j]);
+    const float g = to_f32(gate[t * ld + (group > 1 ? j / group : j)]);
     out[i] = from_f32<T>(to_f32(out[i]) / (1.f + expf(-g)));
   }
 }
 
+// A temperature on the queries that grows with the position p: 1 + coef * ln(floor((p + 1) / every) + 1), float32.
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
+  return 1.f + coef * logf((float)((pos + 1) / every) + 1.f);
+}
+
 // ------------------------------------------------------------------------------------------
 // Whole-projection query/key norm, value blending and the cache write of one attention layer.
+// With temp_every > 0 the queries are also multiplied by query_temperature(position).
 //   proj[t] (row stride ld) = [ q : n_q*hd | k : n_kv*hd | v : n_kv*hdv | ... ]
 //   q_out[t]  = q * rsqrt(mean over ALL n_q*hd elements of q^2 + eps) * q_w      (q_w null: q unchanged)
 //   k' likewise over all n_kv*hd elements with k_w;  v' = v_first ? (1 - lam) v + lam v_first[t] : v
@@ -215,7 +312,7 @@ __global__ void qk_norm_store_kernel(const T* __restrict__ proj, int ld, T* __re
                                      const T* __restrict__ v_first, int v_first_ld, const int* __restrict__ tok_pos,
                                      const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                                      const int* __restrict__ block_table, int max_pages, int page_size, int n_q,
-                                     int n_kv, int hd, int hdv, int write_kv) {
+                                     int n_kv, int hd, int hdv, int write_kv, float temp_coef, int temp_every) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[32];
@@ -237,11 +334,13 @@ __global__ void qk_norm_store_kernel(const T* __restrict__ proj, int ld, T* __re
     ss = block_sum(ss, red);
     rk = 1.f / sqrtf(ss / (float)nk + eps);
   }
+  const int pos = tok_pos[t];
+  const bool temp = temp_every > 0;
+  if (temp) rq *= query_temperature(pos, temp_coef, temp_every);
   T* qo = q_out + (size_t)t * nq;
   for (int i = threadIdx.x; i < nq; i += blockDim.x)
-    qo[i] = q_w ? from_f32<T>(to_f32(qs[i]) * rq * q_w[i]) : qs[i];
+    qo[i] = (q_w || temp) ? from_f32<T>(to_f32(qs[i]) * rq * (q_w ? q_w[i] : 1.f)) : qs[i];
   if (!write_kv) return;
-  const int pos = tok_pos[t];
   const int slot = seq_slot[tok_seq[t]];
   const int page = block_table[(size_t)slot * max_pages + pos / page_size];
   const int in_page = pos % page_size;
@@ -275,7 +374,7 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
                                          int v_first_ld, const int* __restrict__ tok_pos,
                                          const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                                          const int* __restrict__ block_table, int max_pages, int page_size, int n_q,
-                                         int n_kv, int hd, int hdv, int write_kv) {
+                                         int n_kv, int hd, int hdv, int write_kv, float temp_coef, int temp_every) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[2][32];
@@ -285,7 +384,8 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
   const T* ks = qs + nq;
   const T* vs = ks + nk;
   const int i0 = threadIdx.x * 8, step = blockDim.x * 8;
-  const int pos = write_kv ? tok_pos[t] : 0;
+  const bool temp = temp_every > 0;
+  const int pos = (write_kv || temp) ? tok_pos[t] : 0;
   const int sq_idx = write_kv ? tok_seq[t] : 0;
   float q[R][8];
 #pragma unroll
@@ -329,7 +429,8 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
     sq = warp_sum(lane < n_warps ? red[0][lane] : 0.f);
     sk = warp_sum(lane < n_warps ? red[1][lane] : 0.f);
   }
-  const float rq = q_w ? 1.f / sqrtf(sq / (float)nq + eps) : 1.f;
+  float rq = q_w ? 1.f / sqrtf(sq / (float)nq + eps) : 1.f;
+  if (temp) rq *= query_temperature(pos, temp_coef, temp_every);
   const float rk = (k_w && write_kv) ? 1.f / sqrtf(sk / (float)nk + eps) : 1.f;
   T* qo = q_out + (size_t)t * nq;
 #pragma unroll
@@ -341,6 +442,9 @@ __global__ void qk_norm_store_vec_kernel(const T* __restrict__ proj, int ld, T* 
         load8(q_w + i, w8);
 #pragma unroll
         for (int e = 0; e < 8; ++e) q[r][e] = q[r][e] * rq * w8[e];
+      } else if (temp) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q[r][e] *= rq;
       }
       store8(qo + i, q[r]);
     }
@@ -477,14 +581,58 @@ extern "C" int llmie_cast_rows(const float* x, void* out, int out_dtype, long lo
 }
 
 // out[T, n] *= sigmoid(gate[t * ld + j]); both of `dtype`.
-extern "C" int llmie_sigmoid_gate(void* out, const void* gate, int ld, int n_tokens, int n, int dtype,
-                                  cudaStream_t stream) {
-  if (n_tokens < 0 || n <= 0 || ld < n) return LLMIE_ERR_BAD_ARG;
+// `group` > 1: gate rows hold n / group numbers, each for a run of `group` output columns (one gate per head).
+extern "C" int llmie_sigmoid_gate_grouped(void* out, const void* gate, int ld, int n_tokens, int n, int group, int dtype,
+                                          cudaStream_t stream) {
+  if (n_tokens < 0 || n <= 0 || group <= 0 || n % group || ld < n / group) return LLMIE_ERR_BAD_ARG;
   if (n_tokens == 0) return LLMIE_OK;
   const size_t total = (size_t)n_tokens * n;
   const dim3 grid(flat_blocks(total)), block(256);
-  if (dtype == LLMIE_F32) launch_k(sigmoid_gate_kernel<float>, grid, block, 0, stream, (float*)out, (const float*)gate, ld, n, total);
-  else if (dtype == LLMIE_BF16) launch_k(sigmoid_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, ld, n, total);
+  if (dtype == LLMIE_F32) launch_k(sigmoid_gate_kernel<float>, grid, block, 0, stream, (float*)out, (const float*)gate, ld, n, group, total);
+  else if (dtype == LLMIE_BF16) launch_k(sigmoid_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, ld, n, group, total);
+  else return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+extern "C" int llmie_sigmoid_gate(void* out, const void* gate, int ld, int n_tokens, int n, int dtype,
+                                  cudaStream_t stream) {
+  return llmie_sigmoid_gate_grouped(out, gate, ld, n_tokens, n, 1, dtype, stream);
+}
+
+// h float32 [T, d] = norm(alpha * h + s (.) y) * w; y [T, d] of y_dtype; s float32 [d] or null; act of act_dtype or null.
+extern "C" int llmie_scaled_sum_norm(float* h, const void* y, int y_dtype, const float* s, float alpha, const float* w,
+                                     float eps, void* act, int act_dtype, int n_tokens, int d, cudaStream_t stream) {
+  if (n_tokens < 0 || d <= 0 || !w || !y || !h) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (y_dtype != LLMIE_BF16 && y_dtype != LLMIE_F32) return LLMIE_ERR_DTYPE;
+  if (act && act_dtype != LLMIE_BF16 && act_dtype != LLMIE_F32) return LLMIE_ERR_DTYPE;
+  const bool vec = d % 8 == 0 && d <= 8 * 1024 && aligned16(h) && aligned16(y) && aligned16(w) &&
+                   (!s || aligned16(s)) && (!act || aligned16(act));
+  const dim3 grid(n_tokens), block(vec ? ((d / 8 + 31) / 32) * 32 : row_threads(d));
+#define LLMIE_SSN(Y, A)                                                                                                \
+  if (vec) launch_k(scaled_sum_norm_vec_kernel<Y, A>, grid, block, 0, stream, h, (const Y*)y, s, alpha, w, eps, (A*)act, d); \
+  else launch_k(scaled_sum_norm_kernel<Y, A>, grid, block, smem, stream, h, (const Y*)y, s, alpha, w, eps, (A*)act, d)
+  const bool y_bf16 = y_dtype == LLMIE_BF16, act_bf16 = act && act_dtype == LLMIE_BF16;
+  if (y_bf16 && act_bf16) { LLMIE_SSN(__nv_bfloat16, __nv_bfloat16); }
+  else if (y_bf16) { LLMIE_SSN(__nv_bfloat16, float); }
+  else if (act_bf16) { LLMIE_SSN(float, __nv_bfloat16); }
+  else { LLMIE_SSN(float, float); }
+#undef LLMIE_SSN
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// out [T, n] = RMS norm of columns off .. off + n - 1 of src [T, ld], times w float32 [n]; both of `dtype`.
+extern "C" int llmie_rmsnorm_cols(const void* src, int ld, int off, const float* w, float eps, void* out, int n_tokens,
+                                  int n, int dtype, cudaStream_t stream) {
+  if (n_tokens < 0 || n <= 0 || off < 0 || ld < off + n || !w || !src || !out) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const dim3 grid(n_tokens), block(row_threads(n));
+  if (dtype == LLMIE_F32) launch_k(rmsnorm_cols_kernel<float>, grid, block, 0, stream, (const float*)src, ld, off, w, eps, (float*)out, n);
+  else if (dtype == LLMIE_BF16) launch_k(rmsnorm_cols_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)src, ld, off, w, eps, (__nv_bfloat16*)out, n);
   else return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
@@ -493,11 +641,13 @@ extern "C" int llmie_sigmoid_gate(void* out, const void* gate, int ld, int n_tok
 // proj [T, ld]; q_out [T, n_q hd]; k_cache [pages, n_kv, page_size, hd]; v_cache [pages, n_kv, page_size, hdv]; all
 // of `dtype`. q_w, k_w float32 or null; lam_ptr float32 scalar on the device (needed with v_first); v_first rows of
 // n_kv*hdv elements, v_first_ld apart, or null.
-extern "C" int llmie_qk_norm_store(const void* proj, int ld, void* q_out, void* k_cache, void* v_cache, const float* q_w,
-                                   const float* k_w, float eps, const float* lam_ptr, const void* v_first,
-                                   int v_first_ld, const int* tok_pos, const int* tok_seq, const int* seq_slot,
-                                   const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
-                                   int n_kv, int hd, int hdv, int write_kv, int dtype, cudaStream_t stream) {
+// temp_every > 0: the queries are multiplied by 1 + temp_coef * ln(floor((position + 1) / temp_every) + 1).
+extern "C" int llmie_qk_norm_store_temp(const void* proj, int ld, void* q_out, void* k_cache, void* v_cache,
+                                        const float* q_w, const float* k_w, float eps, const float* lam_ptr,
+                                        const void* v_first, int v_first_ld, const int* tok_pos, const int* tok_seq,
+                                        const int* seq_slot, const int* block_table, int max_pages, int page_size,
+                                        int n_tokens, int n_q, int n_kv, int hd, int hdv, int write_kv, int dtype,
+                                        float temp_coef, int temp_every, cudaStream_t stream) {
   if (n_tokens < 0 || n_q <= 0 || n_kv <= 0 || hd <= 0 || hdv <= 0 || page_size <= 0 || max_pages <= 0)
     return LLMIE_ERR_BAD_ARG;
   if (ld < n_q * hd + n_kv * hd + n_kv * hdv) return LLMIE_ERR_BAD_ARG;
@@ -522,7 +672,7 @@ extern "C" int llmie_qk_norm_store(const void* proj, int ld, void* q_out, void* 
 #define LLMIE_QKV(T, R)                                                                                              \
   launch_k(qk_norm_store_vec_kernel<T, R>, grid, vblock, 0, stream, (const T*)proj, ld, (T*)q_out, (T*)k_cache,       \
            (T*)v_cache, q_w, k_w, eps, lam_ptr, (const T*)v_first, v_first_ld, tok_pos, tok_seq, seq_slot, block_table, \
-           max_pages, page_size, n_q, n_kv, hd, hdv, write_kv)
+           max_pages, page_size, n_q, n_kv, hd, hdv, write_kv, temp_coef, temp_every)
     if (dtype == LLMIE_F32) {
       if (per_thread <= 1) LLMIE_QKV(float, 1); else if (per_thread == 2) LLMIE_QKV(float, 2); else LLMIE_QKV(float, 4);
     } else if (dtype == LLMIE_BF16) {
@@ -539,14 +689,24 @@ extern "C" int llmie_qk_norm_store(const void* proj, int ld, void* q_out, void* 
   if (dtype == LLMIE_F32)
     launch_k(qk_norm_store_kernel<float>, grid, block, 0, stream, (const float*)proj, ld, (float*)q_out,
              (float*)k_cache, (float*)v_cache, q_w, k_w, eps, lam_ptr, (const float*)v_first, v_first_ld, tok_pos,
-             tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, hdv, write_kv);
+             tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, hdv, write_kv, temp_coef, temp_every);
   else if (dtype == LLMIE_BF16)
     launch_k(qk_norm_store_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)proj, ld,
              (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, q_w, k_w, eps, lam_ptr,
              (const __nv_bfloat16*)v_first, v_first_ld, tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size,
-             n_q, n_kv, hd, hdv, write_kv);
+             n_q, n_kv, hd, hdv, write_kv, temp_coef, temp_every);
   else
     return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
+}
+
+extern "C" int llmie_qk_norm_store(const void* proj, int ld, void* q_out, void* k_cache, void* v_cache, const float* q_w,
+                                   const float* k_w, float eps, const float* lam_ptr, const void* v_first,
+                                   int v_first_ld, const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                   const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
+                                   int n_kv, int hd, int hdv, int write_kv, int dtype, cudaStream_t stream) {
+  return llmie_qk_norm_store_temp(proj, ld, q_out, k_cache, v_cache, q_w, k_w, eps, lam_ptr, v_first, v_first_ld, tok_pos,
+                                  tok_seq, seq_slot, block_table, max_pages, page_size, n_tokens, n_q, n_kv, hd, hdv,
+                                  write_kv, dtype, 0.f, 0, stream);
 }

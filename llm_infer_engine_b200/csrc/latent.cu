@@ -18,7 +18,8 @@ namespace llmie {
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int dkv_off, T* __restrict__ q_out,
+latent_prepare_kernel(const T* __restrict__ proj, int ld, const T* __restrict__ q_src, int q_ld, int q_off, int dkv_off,
+                      T* __restrict__ q_out,
                       T* __restrict__ cache, const float* __restrict__ norm_w, float eps,
                       const float* __restrict__ table, int table_len, int rot_dims, const int* __restrict__ tok_pos,
                       const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
@@ -59,7 +60,7 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int dkv_off
   const int qw = dim + rot, ow = rank + rot;
   for (int idx = threadIdx.x; idx < n_heads * rot; idx += blockDim.x) {
     const int h = idx / rot, i = idx - h * rot;
-    const T* qr = row + q_off + (size_t)h * qw + dim;
+    const T* qr = q_src + (size_t)t * q_ld + q_off + (size_t)h * qw + dim;
     float v = to_f32(qr[i]);
     if (i < rot_dims) {
       const float c = cs[(i >> 1) * 2], s = cs[(i >> 1) * 2 + 1];
@@ -78,11 +79,15 @@ using namespace llmie;
 // projection at column dkv_off (rank + rot); q_out [T, n_heads * (rank + rot)]: only the last `rot` columns of each head
 // are written here; cache [n_pages, 1, page_size, rank + rot]; all three of `dtype`. norm_w float32 [rank];
 // table float32 [table_len, rot_dims / 2, 2] of (cos, sin).
-extern "C" int llmie_latent_prepare(const void* proj, int ld, int q_off, int dkv_off, void* q_out, void* cache,
-                                    const float* norm_w, float eps, const float* table, int table_len, int rot_dims,
-                                    const int* tok_pos, const int* tok_seq, const int* seq_slot, const int* block_table,
-                                    int max_pages, int page_size, int n_tokens, int n_heads, int dim, int rot, int rank,
-                                    int write, int dtype, cudaStream_t stream) {
+// The queries are read from q_src (rows q_ld apart, column q_off on), which may be another tensor than proj: designs
+// whose queries pass through a latent of their own make them with a second product.
+extern "C" int llmie_latent_prepare_from(const void* proj, int ld, const void* q_src, int q_ld, int q_off, int dkv_off,
+                                         void* q_out, void* cache, const float* norm_w, float eps, const float* table,
+                                         int table_len, int rot_dims, const int* tok_pos, const int* tok_seq,
+                                         const int* seq_slot, const int* block_table, int max_pages, int page_size,
+                                         int n_tokens, int n_heads, int dim, int rot, int rank, int write, int dtype,
+                                         cudaStream_t stream) {
+  if (!q_src || q_ld < q_off + n_heads * (dim + rot)) return LLMIE_ERR_BAD_ARG;
   if (n_tokens < 0 || n_heads <= 0 || dim <= 0 || rot < 0 || rank <= 0 || ld <= 0 || q_off < 0 || page_size <= 0 ||
       max_pages <= 0 || rot_dims < 0 || rot_dims > rot || rot_dims % 2 || table_len <= 0)
     return LLMIE_ERR_BAD_ARG;
@@ -90,9 +95,19 @@ extern "C" int llmie_latent_prepare(const void* proj, int ld, int q_off, int dkv
   if (dtype != LLMIE_F32 && dtype != LLMIE_BF16) return LLMIE_ERR_DTYPE;
   if (n_tokens == 0) return LLMIE_OK;
   if (dtype == LLMIE_F32)
-    launch_k(latent_prepare_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)proj, ld, q_off, dkv_off, (float*)q_out, (float*)cache, norm_w, eps, table, table_len, rot_dims, tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, n_heads, dim, rot, rank, write);
+    launch_k(latent_prepare_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)proj, ld, (const float*)q_src, q_ld, q_off, dkv_off, (float*)q_out, (float*)cache, norm_w, eps, table, table_len, rot_dims, tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, n_heads, dim, rot, rank, write);
   else
-    launch_k(latent_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, stream, (const __nv_bfloat16*)proj, ld, q_off, dkv_off, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, norm_w, eps, table, table_len, rot_dims, tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, n_heads, dim, rot, rank, write);
+    launch_k(latent_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, stream, (const __nv_bfloat16*)proj, ld, (const __nv_bfloat16*)q_src, q_ld, q_off, dkv_off, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, norm_w, eps, table, table_len, rot_dims, tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, n_heads, dim, rot, rank, write);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
+}
+
+extern "C" int llmie_latent_prepare(const void* proj, int ld, int q_off, int dkv_off, void* q_out, void* cache,
+                                    const float* norm_w, float eps, const float* table, int table_len, int rot_dims,
+                                    const int* tok_pos, const int* tok_seq, const int* seq_slot, const int* block_table,
+                                    int max_pages, int page_size, int n_tokens, int n_heads, int dim, int rot, int rank,
+                                    int write, int dtype, cudaStream_t stream) {
+  return llmie_latent_prepare_from(proj, ld, proj, ld, q_off, dkv_off, q_out, cache, norm_w, eps, table, table_len,
+                                   rot_dims, tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, n_tokens,
+                                   n_heads, dim, rot, rank, write, dtype, stream);
 }

@@ -6,6 +6,10 @@
 //             the softmax over the chosen logits alone
 //             second rule (`mode` 1): scores = softmax over ALL logits; the `top` largest of score + correction are chosen
 //             (the correction steers the choice only); weights = the chosen scores / (their sum + 1e-20) * a constant
+//             third rule (`mode` 2): scores = sigmoid(z) one by one; the `top` largest are chosen and the weights are the
+//             chosen scores themselves (times a constant), not normalised
+//   gather    out[p] = weights[pair at p] * x[token at p] for the sorted positions p: for designs whose weight
+//             multiplies what the expert READS (the combine then adds the experts' outputs with weight one)
 //   sort      the (token, choice) pairs grouped by expert into tiles of `tile` positions, padded per expert; one block,
 //             no host involvement, so the step can be captured: sizes are upper bounds, unused tiles say -1
 //   combine   out[t] = sum_k weight[t, k] * y[t * top + k] (+ shared[t]) in float32, in the order of k; a choice whose
@@ -100,7 +104,8 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
       if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
     }
     if (k == 0) first = best;
-    const float p = mode == 1 ? (best_e < n_experts ? sc[best_e] : 0.f) : expf(best - first);
+    const float p = mode == 1 ? (best_e < n_experts ? sc[best_e] : 0.f)
+                    : mode == 2 ? 1.f / (1.f + expf(-best)) : expf(best - first);
     denom += p;
     if ((k & 31) == lane) { mine = p; mine_id = best_e; }
     if (lane == 0 && best_e < n_experts) z[best_e] = -INFINITY;
@@ -115,7 +120,7 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
     }
   }
   __syncwarp();
-  const float inv = mode == 1 ? out_scale / (denom + 1e-20f) : 1.f / denom;
+  const float inv = mode == 1 ? out_scale / (denom + 1e-20f) : mode == 2 ? out_scale : 1.f / denom;
   for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= inv;
 }
 
@@ -180,6 +185,51 @@ __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, cons
   }
 }
 
+// out[p, :] = weights[sorted_pair[p]] * x[sorted_token[p], :] (zeros where sorted_token[p] < 0); the product is formed
+// in float32 and rounded once to the output type.
+template <typename TI, typename TO>
+__global__ void moe_gather_scaled_kernel(const TI* __restrict__ x, const int* __restrict__ sorted_token,
+                                         const int* __restrict__ sorted_pair, const float* __restrict__ weights,
+                                         TO* __restrict__ out, int d, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t pos = i / d;
+    const int c = (int)(i - pos * d);
+    const int r = sorted_token[pos];
+    float v = 0.f;
+    if (r >= 0) v = weights[sorted_pair[pos]] * to_f32(x[(size_t)r * d + c]);
+    out[i] = from_f32<TO>(v);
+  }
+}
+
+// 8 elements a thread (16-byte loads and stores), bfloat16 in and out, d % 8 == 0.
+__global__ void moe_gather_scaled_vec_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_token,
+                                             const int* __restrict__ sorted_pair, const float* __restrict__ weights,
+                                             __nv_bfloat16* __restrict__ out, int d8, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t pos = i / d8;
+    const int c = (int)(i - pos * d8);
+    const int r = sorted_token[pos];
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    if (r >= 0) {
+      const float w = weights[sorted_pair[pos]];
+      load8(x + ((size_t)r * d8 + c) * 8, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] *= w;
+    }
+    store8(out + i * 8, v);
+  }
+}
+
 template <typename TS, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ pair_pos,
                                    const float* __restrict__ weights, const TS* __restrict__ shared_out,
@@ -194,7 +244,7 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
     float s = 0.f;
     for (int k = 0; k < top; ++k) {
       const size_t row = pair_pos ? (size_t)pair_pos[t * top + k] : t * top + k;
-      s = fmaf(weights[t * top + k], to_f32(y[row * d + c]), s);
+      s = fmaf(weights ? weights[t * top + k] : 1.f, to_f32(y[row * d + c]), s);
     }
     if (shared_out) s += to_f32(shared_out[i]);
     out[i] = s;
@@ -238,11 +288,12 @@ using namespace llmie;
 // x [T, d] of x_dtype; w float32 [E, d]; bias float32 [E] or null; ids int32 [T, top]; weights float32 [T, top].
 // mode 0: the rule above (bias added to the logits, softmax over the chosen logits). mode 1: softmax over all logits,
 // choice by score + correction (float32 [E] or null), weights = chosen scores / (their sum + 1e-20) * out_scale.
+// mode 2: weights = sigmoid of the chosen logits * out_scale, not normalised.
 extern "C" int llmie_moe_route_ex(const void* x, int x_dtype, const float* w, const float* bias, int* ids,
                                   float* weights, int n_tokens, int d, int n_experts, int top, int mode,
                                   const float* correction, float out_scale, cudaStream_t stream) {
   if (n_tokens < 0 || d <= 0 || n_experts <= 0 || top <= 0 || top > n_experts) return LLMIE_ERR_BAD_ARG;
-  if (mode != 0 && mode != 1) return LLMIE_ERR_BAD_ARG;
+  if (mode < 0 || mode > 2) return LLMIE_ERR_BAD_ARG;
   if (x_dtype != LLMIE_F32 && x_dtype != LLMIE_BF16) return LLMIE_ERR_DTYPE;
   const size_t smem = ((size_t)d + 2 * (size_t)n_experts) * sizeof(float);
   if (smem > 48 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
@@ -329,6 +380,37 @@ extern "C" int llmie_moe_gather_rows(const void* x, const int* rows, void* out, 
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   launch_k(moe_gather_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, rows, (__nv_bfloat16*)out, d / 8, total);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// out [n_positions, d] of out_dtype = weights[sorted_pair[p]] * x[sorted_token[p]] (zero rows where sorted_token[p] < 0);
+// x [T, d] of x_dtype; weights float32 [T * top] by pair.
+extern "C" int llmie_moe_gather_scaled(const void* x, int x_dtype, const int* sorted_token, const int* sorted_pair,
+                                       const float* weights, void* out, int out_dtype, int n_positions, int d,
+                                       cudaStream_t stream) {
+  if (n_positions < 0 || d <= 0 || !x || !sorted_token || !sorted_pair || !weights || !out) return LLMIE_ERR_BAD_ARG;
+  if ((x_dtype != LLMIE_F32 && x_dtype != LLMIE_BF16) || (out_dtype != LLMIE_F32 && out_dtype != LLMIE_BF16))
+    return LLMIE_ERR_DTYPE;
+  if (n_positions == 0) return LLMIE_OK;
+  if (x_dtype == LLMIE_BF16 && out_dtype == LLMIE_BF16 && d % 8 == 0 && aligned16(x) && aligned16(out)) {
+    const size_t total = (size_t)n_positions * (d / 8);
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    launch_k(moe_gather_scaled_vec_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x,
+             sorted_token, sorted_pair, weights, (__nv_bfloat16*)out, d / 8, total);
+    LLMIE_LAUNCH_CHECK();
+    return LLMIE_OK;
+  }
+  const size_t total = (size_t)n_positions * d;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const dim3 grid((unsigned)blocks), block(256);
+  const bool xb = x_dtype == LLMIE_BF16, ob = out_dtype == LLMIE_BF16;
+  if (xb && ob) launch_k(moe_gather_scaled_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, sorted_token, sorted_pair, weights, (__nv_bfloat16*)out, d, total);
+  else if (xb) launch_k(moe_gather_scaled_kernel<__nv_bfloat16, float>, grid, block, 0, stream, (const __nv_bfloat16*)x, sorted_token, sorted_pair, weights, (float*)out, d, total);
+  else if (ob) launch_k(moe_gather_scaled_kernel<float, __nv_bfloat16>, grid, block, 0, stream, (const float*)x, sorted_token, sorted_pair, weights, (__nv_bfloat16*)out, d, total);
+  else launch_k(moe_gather_scaled_kernel<float, float>, grid, block, 0, stream, (const float*)x, sorted_token, sorted_pair, weights, (float*)out, d, total);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }

@@ -6,6 +6,7 @@
 //                                                                element-wise sweep; alpha is a scalar on the device
 //   gated_act    out = act(gate) * up over [gate | up] rows      act by code (common.cuh: apply_act)
 //   scale_rows   x *= s                                          the logits of designs that scale them
+//   cap_rows     x = c tanh(x / c)                                   the logits of designs that cap them
 //
 // The stream h and all arithmetic are float32 in both precisions; d1, d2 and y have the activation type or float32.
 #include "common.cuh"
@@ -118,6 +119,14 @@ __global__ void scale_rows_kernel(float* __restrict__ x, float s, size_t n) {
   for (; i < n; i += stride) x[i] *= s;
 }
 
+__global__ void cap_rows_kernel(float* __restrict__ x, float c, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) x[i] = c * tanhf(x[i] / c);
+}
+
 static inline int sweep_blocks(size_t items, int threads) {
   size_t b = (items + threads - 1) / threads;
   return (int)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
@@ -191,6 +200,15 @@ extern "C" int llmie_scale_rows(float* x, float s, long long n, cudaStream_t str
   if (n == 0) return LLMIE_OK;
   if (n < 0 || !x) return LLMIE_ERR_BAD_ARG;
   launch_k(scale_rows_kernel, dim3(sweep_blocks((size_t)n, 256)), dim3(256), 0, stream, x, s, (size_t)n);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// x float32 [n] = c tanh(x / c), c > 0.
+extern "C" int llmie_cap_rows(float* x, float c, long long n, cudaStream_t stream) {
+  if (n == 0) return LLMIE_OK;
+  if (n < 0 || !x || !(c > 0.f)) return LLMIE_ERR_BAD_ARG;
+  launch_k(cap_rows_kernel, dim3(sweep_blocks((size_t)n, 256)), dim3(256), 0, stream, x, c, (size_t)n);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }

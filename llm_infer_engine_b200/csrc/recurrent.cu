@@ -9,8 +9,11 @@
 //
 //   matrix_gates       q = silu(q_raw), f = l + (1 - l) sigmoid(f_raw + b)           element-wise, float32 out
 //   matrix_scan        S <- diag(f_t) S + (1 - f_t) v_t^T ; o_t = S^T q_t            S [dim, vdim] per head
+//                      keyed form (a decay per head given): S <- a_h S + k_t v_t^T   linear attention with a constant decay
+//   act_columns        float32 copies of up to three runs of columns of the projections, through an activation
 //   matrix_scan_chunked  the same for long pieces, cut into chunks that run side by side (below)
-//   head_rmsnorm       o / sqrt(mean(o^2) + eps) * w over each head's vdim
+//   head_rmsnorm       o / sqrt(mean(o^2) + eps) * w over each head's vdim (or over the whole row, with a weight per
+//                      column), optionally times sigmoid(gate)
 //   causal_conv        u_t = b + sum_j taps[:, K-1-j] x_(t-j), x before the step from the state's last K-1 inputs
 //   unit_gate_values   a = exp(-c r softplus(lam)), drive = sqrt(1 - a^2) i u, r and i sigmoids of given pre-activations
 //   unit_scan          S <- a_t S + drive_t ; out_t = S act(y_raw + b) ; the new conv state
@@ -56,6 +59,7 @@ constexpr int kScanR = 16;          // state rows a thread keeps at most
 // grid (column tiles, heads, sequences). A thread owns column j of its head's state and the rows [s R, (s+1) R) of it,
 // S = slices (a power of two up to 32, lanes that differ in their low bits), R = ceil(dim / S) <= kScanR. The next
 // token's gate, query and value are requested before the current token's products.
+// With `head_decay` (float32 [H]) the update is S <- head_decay[h] S + k_t v_t^T with the keys k_t in the place of fg.
 // MODE 0: a sequence's whole piece, from the slot's state to the slot's state. MODE 1 and 2 work on chunk c =
 // blockIdx.z % NC of sequence blockIdx.z / NC, L tokens each, with ws float32 [n_seqs, NC, H, D, Dv] and decay float32
 // [n_seqs, NC, H, D]: MODE 1 runs a chunk that is not the sequence's last from a zero state, without outputs, and leaves
@@ -66,8 +70,12 @@ __global__ void __launch_bounds__(kScanThreads)
 matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, const T* __restrict__ v, int v_ld,
                    float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
                    float* __restrict__ o, int H, int D, int Dv, int S, int R, int write_state,
-                   float* __restrict__ ws, float* __restrict__ decay, int L, int NC) {
+                   float* __restrict__ ws, float* __restrict__ decay, int L, int NC,
+                   const float* __restrict__ head_decay) {
   pdl_launch_dependents();
+  // keyed form: fg holds keys k_t instead of gates, and the gate of every row of head h is the constant head_decay[h]
+  const bool keyed = head_decay != nullptr;
+  const float dh = keyed ? head_decay[blockIdx.y] : 0.f;       // a constant of the model: no kernel writes it
   pdl_wait();
   const int s = threadIdx.x & (S - 1);
   const int col = threadIdx.x / S;
@@ -117,8 +125,8 @@ matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, c
     float acc = 0.f;
 #pragma unroll
     for (int r = 0; r < kScanR; ++r) {
-      St[r] = fmaf(cf[r], St[r], (1.f - cf[r]) * cv);
-      if (MODE == 1) prod[r] *= cf[r];
+      St[r] = keyed ? fmaf(dh, St[r], cf[r] * cv) : fmaf(cf[r], St[r], (1.f - cf[r]) * cv);
+      if (MODE == 1) prod[r] *= keyed ? dh : cf[r];
       else acc = fmaf(St[r], cq[r], acc);
     }
     if (MODE != 1) {
@@ -169,10 +177,12 @@ __global__ void matrix_scan_chain_kernel(const float* __restrict__ state, const 
   }
 }
 
-// a warp per (token, head): o float32 [T, H * Dv] -> y of the activation type
+// a warp per (token, head): o float32 [T, H * Dv] -> y of the activation type. `gate` (rows gate_ld apart, null = none):
+// the result is multiplied by sigmoid(gate) of the same place. An item may also be a token's whole row (Dv = the row).
 template <typename T>
 __global__ void head_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
-                                    T* __restrict__ y, int Dv, size_t n_items) {
+                                    T* __restrict__ y, int Dv, size_t n_items, const T* __restrict__ gate, int gate_ld,
+                                    int items_per_row) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t item = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -183,7 +193,37 @@ __global__ void head_rmsnorm_kernel(const float* __restrict__ o, const float* __
   for (int i = lane; i < Dv; i += 32) { const float x = row[i]; ss = fmaf(x, x, ss); }
   ss = warp_sum(ss);
   const float r = 1.f / sqrtf(ss / (float)Dv + eps);
-  for (int i = lane; i < Dv; i += 32) y[item * Dv + i] = from_f32<T>(row[i] * r * w[i]);
+  if (!gate) {
+    for (int i = lane; i < Dv; i += 32) y[item * Dv + i] = from_f32<T>(row[i] * r * w[i]);
+    return;
+  }
+  const size_t t = item / items_per_row;
+  const T* gr = gate + t * gate_ld + (item - t * items_per_row) * Dv;
+  for (int i = lane; i < Dv; i += 32)
+    y[item * Dv + i] = from_f32<T>(row[i] * r * w[i] / (1.f + expf(-to_f32(gr[i]))));
+}
+
+// Float32 copies of up to three runs of columns of proj [T, ld], each through the activation `act`:
+// out_k[t, c] = act(proj[t, off_k + c]), c < n_k. (What a linear-attention layer reads of its projections.)
+template <typename T>
+__global__ void act_columns_kernel(const T* __restrict__ proj, int ld, int off0, int n0, float* __restrict__ out0,
+                                   int off1, int n1, float* __restrict__ out1, int off2, int n2,
+                                   float* __restrict__ out2, int act, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = n0 + n1 + n2;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / n;
+    int c = (int)(i - t * n);
+    const T* row = proj + t * ld;
+    if (c < n0) { out0[t * n0 + c] = apply_act(to_f32(row[off0 + c]), act); continue; }
+    c -= n0;
+    if (c < n1) { out1[t * n1 + c] = apply_act(to_f32(row[off1 + c]), act); continue; }
+    c -= n1;
+    out2[t * n2 + c] = apply_act(to_f32(row[off2 + c]), act);
+  }
 }
 
 // ------------------------------------------------------------------------------------------ vector state
@@ -456,9 +496,10 @@ extern "C" int llmie_matrix_gates(const void* proj, int ld, int q_off, int f_off
 
 // qa, fg float32 [T, H * D]; v rows of H * Dv elements of `dtype`, v_ld apart; state float32 [slots, H, D, Dv];
 // o float32 [T, H * Dv]. D up to 512.
-extern "C" int llmie_matrix_scan(const float* qa, const float* fg, const void* v, int v_ld, float* state,
-                                 const int* cu_q, const int* seq_slot, float* o, int n_seqs, int H, int D, int Dv,
-                                 int write_state, int dtype, cudaStream_t stream) {
+// head_decay float32 [H] or null: with it, fg holds keys and S <- head_decay[h] S + k_t v_t^T.
+extern "C" int llmie_matrix_scan_ex(const float* qa, const float* fg, const void* v, int v_ld, float* state,
+                                    const int* cu_q, const int* seq_slot, float* o, int n_seqs, int H, int D, int Dv,
+                                    int write_state, int dtype, const float* head_decay, cudaStream_t stream) {
   if (n_seqs < 0 || H <= 0 || D <= 0 || Dv <= 0 || v_ld < H * Dv) return LLMIE_ERR_BAD_ARG;
   if (D > 32 * kScanR) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (n_seqs == 0) return LLMIE_OK;
@@ -470,38 +511,45 @@ extern "C" int llmie_matrix_scan(const float* qa, const float* fg, const void* v
   if (grid.y > 65535 || grid.z > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (dtype == LLMIE_F32)
     launch_k(matrix_scan_kernel<float, 0>, grid, block, 0, stream, qa, fg, (const float*)v, v_ld, state, cu_q, seq_slot,
-             o, H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1);
+             o, H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1, head_decay);
   else if (dtype == LLMIE_BF16)
     launch_k(matrix_scan_kernel<__nv_bfloat16, 0>, grid, block, 0, stream, qa, fg, (const __nv_bfloat16*)v, v_ld, state,
-             cu_q, seq_slot, o, H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1);
+             cu_q, seq_slot, o, H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1, head_decay);
   else
     return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
 
+extern "C" int llmie_matrix_scan(const float* qa, const float* fg, const void* v, int v_ld, float* state,
+                                 const int* cu_q, const int* seq_slot, float* o, int n_seqs, int H, int D, int Dv,
+                                 int write_state, int dtype, cudaStream_t stream) {
+  return llmie_matrix_scan_ex(qa, fg, v, v_ld, state, cu_q, seq_slot, o, n_seqs, H, D, Dv, write_state, dtype, nullptr,
+                              stream);
+}
+
 template <typename T>
 static void matrix_scan_chunked_launch(const float* qa, const float* fg, const T* v, int v_ld, float* state,
                                        const int* cu_q, const int* seq_slot, float* o, float* ws, float* decay,
                                        int n_seqs, int H, int D, int Dv, int S, int R, int L, int NC, int write_state,
-                                       cudaStream_t stream) {
+                                       const float* head_decay, cudaStream_t stream) {
   const int cols = kScanThreads / S;
   const dim3 grid((Dv + cols - 1) / cols, H, n_seqs * NC), block(kScanThreads);
   launch_k(matrix_scan_kernel<T, 1>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
-           write_state, ws, decay, L, NC);
+           write_state, ws, decay, L, NC, head_decay);
   const size_t HDDv = (size_t)H * D * Dv;
   launch_k(matrix_scan_chain_kernel, dim3((unsigned)((HDDv + 255) / 256), n_seqs), dim3(256), 0, stream,
            (const float*)state, cu_q, seq_slot, ws, (const float*)decay, H, D, Dv, L, NC);
   launch_k(matrix_scan_kernel<T, 2>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
-           write_state, ws, decay, L, NC);
+           write_state, ws, decay, L, NC, head_decay);
 }
 
 // llmie_matrix_scan for long pieces: chunks of `chunk` tokens run side by side. n_chunks >= ceil(longest piece / chunk);
 // ws float32 [n_seqs, n_chunks, H, D, Dv] and decay float32 [n_seqs, n_chunks, H, D] are scratch.
-extern "C" int llmie_matrix_scan_chunked(const float* qa, const float* fg, const void* v, int v_ld, float* state,
-                                         const int* cu_q, const int* seq_slot, float* o, float* ws, float* decay,
-                                         int n_seqs, int H, int D, int Dv, int chunk, int n_chunks, int write_state,
-                                         int dtype, cudaStream_t stream) {
+extern "C" int llmie_matrix_scan_chunked_ex(const float* qa, const float* fg, const void* v, int v_ld, float* state,
+                                            const int* cu_q, const int* seq_slot, float* o, float* ws, float* decay,
+                                            int n_seqs, int H, int D, int Dv, int chunk, int n_chunks, int write_state,
+                                            int dtype, const float* head_decay, cudaStream_t stream) {
   if (n_seqs < 0 || H <= 0 || D <= 0 || Dv <= 0 || v_ld < H * Dv || chunk <= 0 || n_chunks <= 0 || !ws || !decay)
     return LLMIE_ERR_BAD_ARG;
   if (D > 32 * kScanR) return LLMIE_ERR_UNSUPPORTED_SIZE;
@@ -512,10 +560,39 @@ extern "C" int llmie_matrix_scan_chunked(const float* qa, const float* fg, const
   if (H > 65535 || (long long)n_seqs * n_chunks > 65535 || n_seqs > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (dtype == LLMIE_F32)
     matrix_scan_chunked_launch(qa, fg, (const float*)v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D, Dv, S,
-                               R, chunk, n_chunks, write_state, stream);
+                               R, chunk, n_chunks, write_state, head_decay, stream);
   else if (dtype == LLMIE_BF16)
     matrix_scan_chunked_launch(qa, fg, (const __nv_bfloat16*)v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D,
-                               Dv, S, R, chunk, n_chunks, write_state, stream);
+                               Dv, S, R, chunk, n_chunks, write_state, head_decay, stream);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+extern "C" int llmie_matrix_scan_chunked(const float* qa, const float* fg, const void* v, int v_ld, float* state,
+                                         const int* cu_q, const int* seq_slot, float* o, float* ws, float* decay,
+                                         int n_seqs, int H, int D, int Dv, int chunk, int n_chunks, int write_state,
+                                         int dtype, cudaStream_t stream) {
+  return llmie_matrix_scan_chunked_ex(qa, fg, v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D, Dv, chunk,
+                                      n_chunks, write_state, dtype, nullptr, stream);
+}
+
+// proj [T, ld] of `dtype`; out_k float32 [T, n_k] = act(proj[:, off_k : off_k + n_k]) for up to three runs (n_k = 0: unused).
+extern "C" int llmie_act_columns(const void* proj, int ld, int off0, int n0, float* out0, int off1, int n1, float* out1,
+                                 int off2, int n2, float* out2, int act, int n_tokens, int dtype, cudaStream_t stream) {
+  if (n_tokens < 0 || n0 <= 0 || n1 < 0 || n2 < 0 || off0 < 0 || off1 < 0 || off2 < 0) return LLMIE_ERR_BAD_ARG;
+  if (ld < off0 + n0 || (n1 && ld < off1 + n1) || (n2 && ld < off2 + n2)) return LLMIE_ERR_BAD_ARG;
+  if (!out0 || (n1 && !out1) || (n2 && !out2)) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const size_t total = (size_t)n_tokens * (n0 + n1 + n2);
+  const dim3 grid(sweep_blocks(total, 256)), block(256);
+  if (dtype == LLMIE_F32)
+    launch_k(act_columns_kernel<float>, grid, block, 0, stream, (const float*)proj, ld, off0, n0, out0, off1, n1, out1,
+             off2, n2, out2, act, total);
+  else if (dtype == LLMIE_BF16)
+    launch_k(act_columns_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)proj, ld, off0, n0, out0,
+             off1, n1, out1, off2, n2, out2, act, total);
   else
     return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
@@ -523,23 +600,31 @@ extern "C" int llmie_matrix_scan_chunked(const float* qa, const float* fg, const
 }
 
 // o float32 [n_items, Dv] (an item = a token's head); w float32 [Dv]; y [n_items, Dv] of `dtype`.
-extern "C" int llmie_head_rmsnorm(const float* o, const float* w, float eps, void* y, long long n_items, int Dv,
-                                  int dtype, cudaStream_t stream) {
-  if (n_items < 0 || Dv <= 0) return LLMIE_ERR_BAD_ARG;
+// gate (of `dtype`, rows gate_ld apart, items_per_row items a row) or null: y is also multiplied by sigmoid(gate).
+extern "C" int llmie_head_rmsnorm_gated(const float* o, const float* w, float eps, void* y, long long n_items, int Dv,
+                                        int dtype, const void* gate, int gate_ld, int items_per_row,
+                                        cudaStream_t stream) {
+  if (n_items < 0 || Dv <= 0 || (gate && (items_per_row <= 0 || gate_ld < items_per_row * Dv))) return LLMIE_ERR_BAD_ARG;
   if (n_items == 0) return LLMIE_OK;
   const int warps = 4;
   const long long blocks = (n_items + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return LLMIE_ERR_UNSUPPORTED_SIZE;
   const dim3 grid((unsigned)blocks), block(warps * 32);
   if (dtype == LLMIE_F32)
-    launch_k(head_rmsnorm_kernel<float>, grid, block, 0, stream, o, w, eps, (float*)y, Dv, (size_t)n_items);
+    launch_k(head_rmsnorm_kernel<float>, grid, block, 0, stream, o, w, eps, (float*)y, Dv, (size_t)n_items,
+             (const float*)gate, gate_ld, items_per_row);
   else if (dtype == LLMIE_BF16)
     launch_k(head_rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, stream, o, w, eps, (__nv_bfloat16*)y, Dv,
-             (size_t)n_items);
+             (size_t)n_items, (const __nv_bfloat16*)gate, gate_ld, items_per_row);
   else
     return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
+}
+
+extern "C" int llmie_head_rmsnorm(const float* o, const float* w, float eps, void* y, long long n_items, int Dv,
+                                  int dtype, cudaStream_t stream) {
+  return llmie_head_rmsnorm_gated(o, w, eps, y, n_items, Dv, dtype, nullptr, 0, 1, stream);
 }
 
 // proj [T, ld] of `dtype` with the convolution's input at column x_off (C columns); x_bias, conv_bias float32 [C] or

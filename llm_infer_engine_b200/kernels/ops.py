@@ -401,25 +401,69 @@ def cast_rows(x, out):
     return out
 
 
-def sigmoid_gate(out, gate):
-    """out[T, n] *= sigmoid(gate[T, n]); gate may be a column slice of a wider tensor."""
+def sigmoid_gate(out, gate, group: int = 1):
+    """out[T, n] *= sigmoid(gate[T, n / group]) with every gate serving a run of `group` columns (group 1: a gate per
+    element; group = a head's value size: one gate per head); gate may be a column slice of a wider tensor."""
     T, n = out.shape
     _need(out, "out")
-    ld = _row_slice(gate, "gate", out.dtype, T, n)
-    _work(2 * _nbytes(out) + T * n * out.element_size())
-    f = _fn("branch_elementwise", "llmie_sigmoid_gate", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p])
-    _check(f(out.data_ptr(), gate.data_ptr(), ld, T, n, _dt(out, "out"), _stream()), "sigmoid_gate")
+    if group <= 0 or n % group:
+        raise KernelError(f"sigmoid_gate: rows of {n} elements are not whole groups of {group}")
+    ld = _row_slice(gate, "gate", out.dtype, T, n // group)
+    _work(2 * _nbytes(out) + T * (n // group) * out.element_size())
+    f = _fn("branch_elementwise", "llmie_sigmoid_gate_grouped",
+            [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(out.data_ptr(), gate.data_ptr(), ld, T, n, int(group), _dt(out, "out"), _stream()), "sigmoid_gate")
+    return out
+
+
+def scaled_sum_norm(h, y, scale, alpha: float, weight, eps: float, act=None):
+    """Norm after the residual sum: h (float32 [T, d]) = rmsnorm(alpha * h + scale (.) y) * weight, in place. y [T, d]
+    float32 or bfloat16; scale float32 [d] (a learned number per channel) or None; act (optional [T, d]) receives the
+    new h rounded to its dtype."""
+    T, d = h.shape
+    _need(h, "h", torch.float32)
+    _need(y, "y", None, (T, d))
+    _need(weight, "weight", torch.float32, (d,))
+    if scale is not None:
+        _need(scale, "scale", torch.float32, (d,))
+    if act is not None:
+        _need(act, "act", None, (T, d))
+    _work(2 * _nbytes(h) + _nbytes(y, act))
+    f = _fn("branch_elementwise", "llmie_scaled_sum_norm",
+            [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_int,
+             _c_void_p])
+    _check(f(h.data_ptr(), y.data_ptr(), _dt(y, "y"), _ptr(scale), float(alpha), weight.data_ptr(), float(eps),
+             _ptr(act), _dt(act, "act") if act is not None else 0, T, d, _stream()), "scaled_sum_norm")
+    return h
+
+
+def rmsnorm_cols(src, off: int, n: int, weight, eps: float, out):
+    """out [T, n] = RMS norm of the columns off .. off + n - 1 of src [T, ld], times weight float32 [n]; float32
+    arithmetic, out of src's dtype."""
+    T, ld = src.shape
+    _need(src, "src")
+    _need(out, "out", src.dtype, (T, n))
+    _need(weight, "weight", torch.float32, (n,))
+    if off < 0 or off + n > ld:
+        raise KernelError("rmsnorm_cols: the columns do not fit the rows of src")
+    _work(T * n * 2 * src.element_size())
+    f = _fn("branch_elementwise", "llmie_rmsnorm_cols",
+            [_c_void_p, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(src.data_ptr(), ld, int(off), weight.data_ptr(), float(eps), out.data_ptr(), T, n, _dt(src, "src"),
+             _stream()), "rmsnorm_cols")
     return out
 
 
 def qk_norm_store(proj, q_out, k_cache, v_cache, q_w, k_w, eps: float, tok_pos, tok_seq, seq_slot, block_table,
                   page_size: int, n_q: int, n_kv: int, head_dim: int, v_head_dim: int, write_kv: bool = True,
-                  lam: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None):
+                  lam: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None,
+                  temp_coef: float = 0.0, temp_every: int = 0):
     """RMS norm over the WHOLE query projection and over the whole key projection (not per head), value blending,
     and the cache write. proj [T, >= n_q hd + n_kv hd + n_kv hdv] holds [q | k | v | ...] per row; q_out [T, n_q hd];
     q_w / k_w float32 weights of the norms (None: that projection is copied as it is); with `v_first` (rows of
     n_kv hdv values, possibly a column slice) the stored values are (1 - lam) v + lam v_first, lam a float32 scalar
-    on the device."""
+    on the device. With `temp_every` > 0 the queries of position p are also multiplied by
+    1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (a temperature that grows with the position)."""
     T, ld = proj.shape
     nq, nk, nv = n_q * head_dim, n_kv * head_dim, n_kv * v_head_dim
     _need(proj, "proj")
@@ -446,14 +490,14 @@ def qk_norm_store(proj, q_out, k_cache, v_cache, q_w, k_w, eps: float, tok_pos, 
         if lam.numel() != 1:
             raise KernelError("qk_norm_store: lam must hold one number")
     _work((T * (nq + nk + nv) + T * nq + (T * (nk + nv) if write_kv else 0)) * proj.element_size())
-    f = _fn("branch_elementwise", "llmie_qk_norm_store",
+    f = _fn("branch_elementwise", "llmie_qk_norm_store_temp",
             [_c_void_p, _c_int] + [_c_void_p] * 5 + [_c_float, _c_void_p, _c_void_p, _c_int] + [_c_void_p] * 4 +
-            [_c_int] * 9 + [_c_void_p])
+            [_c_int] * 9 + [_c_float, _c_int, _c_void_p])
     _check(f(proj.data_ptr(), ld, q_out.data_ptr(), _ptr(k_cache) if write_kv else None,
              _ptr(v_cache) if write_kv else None, _ptr(q_w), _ptr(k_w), float(eps), _ptr(lam) if v_first is not None else None,
              _ptr(v_first), vf_ld, tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(),
              block_table.shape[1], page_size, T, n_q, n_kv, head_dim, v_head_dim, 1 if write_kv else 0,
-             _dt(proj, "proj"), _stream()), "qk_norm_store")
+             _dt(proj, "proj"), float(temp_coef), int(temp_every), _stream()), "qk_norm_store")
     return q_out
 
 
@@ -1180,6 +1224,17 @@ def scale_rows(x: torch.Tensor, scale: float) -> torch.Tensor:
     return x
 
 
+def cap_rows(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x = cap * tanh(x / cap) in place; x float32, cap > 0."""
+    _need(x, "x", torch.float32)
+    if not cap > 0:
+        raise KernelError(f"cap_rows: the cap must be positive, got {cap}")
+    _work(2 * _nbytes(x))
+    f = _fn("parallel_elementwise", "llmie_cap_rows", [_c_void_p, _c_float, ctypes.c_longlong, _c_void_p])
+    _check(f(x.data_ptr(), float(cap), x.numel(), _stream()), "cap_rows")
+    return x
+
+
 # ------------------------------------------------------------------------------------------ grouped products
 _c_ll = ctypes.c_longlong
 _GROUPED_ARGS = [_c_void_p, _c_ll, _c_ll, _c_void_p, _c_void_p, _c_ll, _c_ll, _c_void_p, _c_ll, _c_ll, _c_void_p,
@@ -1255,12 +1310,17 @@ def routed_gemm_nt(a, a_rows, w, out, out_rows, tile_group, n_positions: int, sm
 
 
 # ------------------------------------------------------------------------------------------ routed feed-forward
-def moe_route(x, w, bias, ids, weights, scores_over_all: bool = False, correction=None, out_scale: float = 1.0):
+ROUTE_SOFTMAX_TOP, ROUTE_SOFTMAX_ALL, ROUTE_SIGMOID = 0, 1, 2
+
+
+def moe_route(x, w, bias, ids, weights, scores_over_all=False, correction=None, out_scale: float = 1.0):
     """Router of a mixture of experts: logits = x @ w^T + bias in float32; ids int32 [T, top] receive the `top`
     largest (ties: the lower index), weights float32 [T, top] the softmax over those logits alone.
     x [T, d] float32 or bfloat16; w float32 [E, d]; bias float32 [E] or None.
     `scores_over_all`: the scores are the softmax over ALL logits, the choice goes by score + correction (float32 [E]
-    or None) and the weights are the chosen scores / (their sum + 1e-20) * out_scale."""
+    or None) and the weights are the chosen scores / (their sum + 1e-20) * out_scale. `scores_over_all` may also be one
+    of the ROUTE_* codes; ROUTE_SIGMOID: the `top` largest logits choose and the weights are sigmoid(logit) * out_scale of
+    the chosen ones, not normalised."""
     T, d = x.shape
     E = w.shape[0]
     top = ids.shape[1]
@@ -1276,7 +1336,7 @@ def moe_route(x, w, bias, ids, weights, scores_over_all: bool = False, correctio
     f = _fn("moe", "llmie_moe_route_ex", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p] + [_c_int] * 5 +
             [_c_void_p, _c_float, _c_void_p])
     _check(f(x.data_ptr(), _dt(x, "x"), w.data_ptr(), _ptr(bias), ids.data_ptr(), weights.data_ptr(), T, d, E, top,
-             1 if scores_over_all else 0, _ptr(correction), float(out_scale), _stream()), "moe_route")
+             int(scores_over_all), _ptr(correction), float(out_scale), _stream()), "moe_route")
 
 
 def moe_max_tiles(n_pairs: int, n_experts: int, tile: int) -> int:
@@ -1307,11 +1367,15 @@ def moe_sort(ids, n_experts: int, tile: int, sorted_token, sorted_pair, tile_gro
 def moe_combine(y, weights, shared_out, out, pair_pos=None):
     """out[t] = sum_k weights[t, k] * y[row of pair t * top + k] (+ shared_out[t]); the row of a pair is the pair's
     own number, or pair_pos[pair] when that is given (y then holds the pairs in sorted order). y float32 or bfloat16
-    [rows, d]; out float32 [T, d]."""
-    T, top = weights.shape
+    [rows, d]; out float32 [T, d]. `weights` may be the number of choices a token (an int) instead of a tensor: every
+    weight is then one (designs whose weight has already multiplied what the expert read)."""
     d = out.shape[1]
+    if isinstance(weights, int):
+        T, top, weights = out.shape[0], weights, None
+    else:
+        T, top = weights.shape
+        _need(weights, "weights", torch.float32)
     _need(y, "y", None, (None if pair_pos is not None else T * top, d))
-    _need(weights, "weights", torch.float32)
     _need(out, "out", torch.float32, (T, d))
     if shared_out is not None:
         _need(shared_out, "shared_out", None, (T, d))
@@ -1320,7 +1384,7 @@ def moe_combine(y, weights, shared_out, out, pair_pos=None):
     _work(T * top * d * y.element_size() + _nbytes(weights, shared_out, out))
     f = _fn("moe", "llmie_moe_combine", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                          _c_int, _c_int, _c_void_p])
-    _check(f(y.data_ptr(), _dt(y, "y"), _ptr(pair_pos), weights.data_ptr(), _ptr(shared_out),
+    _check(f(y.data_ptr(), _dt(y, "y"), _ptr(pair_pos), _ptr(weights), _ptr(shared_out),
              _dt(shared_out, "shared_out") if shared_out is not None else 0, out.data_ptr(), T, d, top, _stream()),
            "moe_combine")
     return out
@@ -1361,6 +1425,26 @@ def moe_gather_rows(x, rows, out):
     return out
 
 
+def moe_gather_scaled(x, sorted_token, sorted_pair, weights, out):
+    """out[p] = weights[sorted_pair[p]] * x[sorted_token[p]] (zeros where sorted_token[p] < 0): the rows of the sorted
+    positions, each times its pair's weight (float32 product, one rounding). x [T, d] and out [P, d] float32 or
+    bfloat16; weights float32 [T, top]."""
+    P, d = out.shape
+    _need(x, "x", None, (None, d))
+    _need(out, "out")
+    _need(sorted_token, "sorted_token", torch.int32)
+    _need(sorted_pair, "sorted_pair", torch.int32)
+    _need(weights, "weights", torch.float32)
+    if sorted_token.shape[0] < P or sorted_pair.shape[0] < P:
+        raise KernelError("moe_gather_scaled: index arrays shorter than the output")
+    _work(2 * _nbytes(out))
+    f = _fn("moe", "llmie_moe_gather_scaled", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                               _c_int, _c_int, _c_void_p])
+    _check(f(x.data_ptr(), _dt(x, "x"), sorted_token.data_ptr(), sorted_pair.data_ptr(), weights.data_ptr(),
+             out.data_ptr(), _dt(out, "out"), P, d, _stream()), "moe_gather_scaled")
+    return out
+
+
 def library_grouped_mm(x: torch.Tensor, w: torch.Tensor, group_end: torch.Tensor) -> torch.Tensor:
     """Rows [group_end[e-1], group_end[e]) of x [P, K] times w[e]^T (w [E, N, K]) through the library's grouped GEMM
     (bfloat16 in and out, float32 accumulation); rows beyond group_end[-1] are left as they are. Like `library_mm`
@@ -1385,27 +1469,32 @@ def library_grouped_mm_ok(n_pairs: int, w_gate_up: torch.Tensor, w_down: torch.T
 # ------------------------------------------------------------------------------------------ latent attention
 def latent_prepare(proj, q_off: int, dkv_off: int, q_out, cache, norm_w, eps: float, table, rot_dims: int, tok_pos,
                    tok_seq, seq_slot, block_table, page_size: int, n_heads: int, dim: int, rot: int, rank: int,
-                   write: bool):
+                   write: bool, q_src=None):
     """Per token: the latent's RMS norm, the rotation of the shared key part and of every head's rotated query part,
     the cache write (rows [latent | rotated key part]) and the rotated query parts into the last `rot` columns of each
     head of q_out [T, n_heads (rank + rot)]. proj [T, ld] holds the queries from column q_off (heads of dim + rot) and,
-    if `write`, the latent projection from dkv_off (rank + rot). table float32 [P, rot_dims / 2, 2] of (cos, sin)."""
+    if `write`, the latent projection from dkv_off (rank + rot). table float32 [P, rot_dims / 2, 2] of (cos, sin).
+    `q_src` ([T, >= q_off + n_heads (dim + rot)], proj's dtype): the queries are read from there instead of proj."""
     T, ld = proj.shape
     _need(proj, "proj")
+    qs = proj if q_src is None else q_src
+    if q_src is not None:
+        _need(q_src, "q_src", proj.dtype, (T, None))
     _need(q_out, "q_out", proj.dtype, (T, n_heads * (rank + rot)))
     _need(table, "table", torch.float32, (None, rot_dims // 2, 2))
     for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot), ("block_table", block_table)):
         _need(t, name, torch.int32)
-    if q_off + n_heads * (dim + rot) > ld or (write and dkv_off + rank + rot > ld):
+    if q_off + n_heads * (dim + rot) > qs.shape[1] or (write and dkv_off + rank + rot > ld):
         raise KernelError("latent_prepare: the projections do not fit the rows of proj")
     if write:
         _need(cache, "cache", proj.dtype, (None, 1, page_size, rank + rot))
         _need(norm_w, "norm_w", torch.float32, (rank,))
     _work(T * (n_heads * 2 * rot + (2 * (rank + rot) if write else 0)) * proj.element_size())
-    f = _fn("latent", "llmie_latent_prepare",
-            [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_int] +
-            [_c_void_p] * 4 + [_c_int] * 9 + [_c_void_p])
-    _check(f(proj.data_ptr(), ld, q_off, dkv_off if write else 0, q_out.data_ptr(), _ptr(cache) if write else None,
+    f = _fn("latent", "llmie_latent_prepare_from",
+            [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p,
+             _c_int, _c_int] + [_c_void_p] * 4 + [_c_int] * 9 + [_c_void_p])
+    _check(f(proj.data_ptr(), ld, qs.data_ptr(), qs.shape[1], q_off, dkv_off if write else 0, q_out.data_ptr(),
+             _ptr(cache) if write else None,
              _ptr(norm_w) if write else None, float(eps), table.data_ptr(), table.shape[0], rot_dims,
              tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              page_size, T, n_heads, dim, rot, rank, 1 if write else 0, _dt(proj, "proj"), _stream()), "latent_prepare")
@@ -1550,14 +1639,17 @@ SCAN_SCRATCH_BYTES = 1 << 30
 
 
 def matrix_scan(q, f, v, state, cu_q, seq_slot, out, n_seqs: int, heads: int, dim: int, vdim: int,
-                write_state: bool = True, max_len: int = 0):
+                write_state: bool = True, max_len: int = 0, head_decay: Optional[torch.Tensor] = None):
     """Per sequence and head, from the state S [dim, vdim] the slot holds: S <- diag(f_t) S + (1 - f_t) v_t^T and
     out_t = S^T q_t for each of the step's tokens in order; the new S is written back. q, f float32 [T, heads dim];
     v [T, heads vdim] (possibly a column slice) float32 or bfloat16; state float32 [slots, heads, dim, vdim];
     out float32 [T, heads vdim]. `max_len`: an upper bound of the longest piece, if the caller knows one; long pieces
     are cut into chunks that run side by side (each chunk from zero, a chain over the chunks' ends, each chunk again
-    from its true start), which changes rounding only."""
+    from its true start), which changes rounding only. With `head_decay` (float32 [heads]) the recurrence is the
+    keyed one, S <- head_decay[h] S + k_t v_t^T, and `f` holds the keys k (linear attention with a constant decay)."""
     T = q.shape[0]
+    if head_decay is not None:
+        _need(head_decay, "head_decay", torch.float32, (heads,))
     _need(q, "q", torch.float32, (T, heads * dim))
     _need(f, "f", torch.float32, (T, heads * dim))
     _need(state, "state", torch.float32, (None, heads, dim, vdim))
@@ -1576,34 +1668,60 @@ def matrix_scan(q, f, v, state, cu_q, seq_slot, out, n_seqs: int, heads: int, di
             ws = torch.empty((n_seqs, n_chunks, heads, dim, vdim), dtype=torch.float32, device=q.device)
             decay = torch.empty((n_seqs, n_chunks, heads, dim), dtype=torch.float32, device=q.device)
             _work(3.0 * _nbytes(ws) + _nbytes(f) + T * heads * vdim * v.element_size(), 4.0 * T * heads * dim * vdim)
-            f_ = _fn("recurrent", "llmie_matrix_scan_chunked",
-                     [_c_void_p, _c_void_p, _c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 8 + [_c_void_p])
+            f_ = _fn("recurrent", "llmie_matrix_scan_chunked_ex",
+                     [_c_void_p, _c_void_p, _c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 8 + [_c_void_p, _c_void_p])
             _check(f_(q.data_ptr(), f.data_ptr(), v.data_ptr(), v_ld, state.data_ptr(), cu_q.data_ptr(),
                       seq_slot.data_ptr(), out.data_ptr(), ws.data_ptr(), decay.data_ptr(), n_seqs, heads, dim, vdim,
-                      chunk, n_chunks, 1 if write_state else 0, _dt(v, "v"), _stream()), "matrix_scan_chunked")
+                      chunk, n_chunks, 1 if write_state else 0, _dt(v, "v"), _ptr(head_decay), _stream()),
+                   "matrix_scan_chunked")
             return out
-    f_ = _fn("recurrent", "llmie_matrix_scan", [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
-                                                _c_void_p] + [_c_int] * 6 + [_c_void_p])
+    f_ = _fn("recurrent", "llmie_matrix_scan_ex", [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                                   _c_void_p, _c_void_p] + [_c_int] * 6 + [_c_void_p, _c_void_p])
     _check(f_(q.data_ptr(), f.data_ptr(), v.data_ptr(), v_ld, state.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(),
-              out.data_ptr(), n_seqs, heads, dim, vdim, 1 if write_state else 0, _dt(v, "v"), _stream()), "matrix_scan")
+              out.data_ptr(), n_seqs, heads, dim, vdim, 1 if write_state else 0, _dt(v, "v"), _ptr(head_decay),
+              _stream()), "matrix_scan")
     return out
 
 
-def head_rmsnorm(o, weight, eps: float, out, vdim: int):
-    """out = o / sqrt(mean(o^2) + eps) * weight over every run of vdim columns (a head); o float32 [T, heads vdim];
-    weight float32 [vdim]; out of the activation type."""
+def head_rmsnorm(o, weight, eps: float, out, vdim: int, gate=None):
+    """out = o / sqrt(mean(o^2) + eps) * weight over every run of vdim columns (a head; vdim = the row's width: the
+    concatenated heads together, with a weight per column); o float32 [T, heads vdim]; weight float32 [vdim]; out of
+    the activation type. `gate` ([T, heads vdim] of out's type, possibly a column slice): out is also multiplied by
+    sigmoid(gate)."""
     T, n = o.shape
     _need(o, "o", torch.float32)
     _need(weight, "weight", torch.float32, (vdim,))
     _need(out, "out", None, (T, n))
     if n % vdim:
         raise KernelError("head_rmsnorm: the row is not a whole number of heads")
-    _work(_nbytes(o, out))
-    f = _fn("recurrent", "llmie_head_rmsnorm", [_c_void_p, _c_void_p, _c_float, _c_void_p, ctypes.c_longlong, _c_int,
-                                                _c_int, _c_void_p])
+    gate_ld = _row_slice(gate, "gate", out.dtype, T, n) if gate is not None else 0
+    _work(_nbytes(o, out) + (T * n * out.element_size() if gate is not None else 0))
+    f = _fn("recurrent", "llmie_head_rmsnorm_gated", [_c_void_p, _c_void_p, _c_float, _c_void_p, ctypes.c_longlong, _c_int,
+                                                      _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
     _check(f(o.data_ptr(), weight.data_ptr(), float(eps), out.data_ptr(), T * (n // vdim), vdim, _dt(out, "out"),
-             _stream()), "head_rmsnorm")
+             _ptr(gate), gate_ld, n // vdim, _stream()), "head_rmsnorm")
     return out
+
+
+def act_columns(proj, runs, act: int):
+    """Float32 copies of up to three runs of columns of proj [T, ld] (float32 or bfloat16), each through the activation
+    `act` (an ACT_* code): `runs` is a list of (first column, float32 out [T, n]); out[t, c] = act(proj[t, first + c])."""
+    T, ld = proj.shape
+    _need(proj, "proj")
+    if not 1 <= len(runs) <= 3:
+        raise KernelError("act_columns: one to three runs of columns")
+    args = []
+    for off, out in runs:
+        _need(out, "out", torch.float32, (T, None))
+        if off < 0 or off + out.shape[1] > ld:
+            raise KernelError("act_columns: a run of columns does not fit the rows of proj")
+        args += [int(off), out.shape[1], out.data_ptr()]
+    args += [0, 0, None] * (3 - len(runs))
+    total = sum(out.shape[1] for _, out in runs)
+    _work(T * total * (proj.element_size() + 4))
+    f = _fn("recurrent", "llmie_act_columns", [_c_void_p, _c_int] + [_c_int, _c_int, _c_void_p] * 3 +
+            [_c_int, _c_int, _c_int, _c_void_p])
+    _check(f(proj.data_ptr(), ld, *args, int(act), T, _dt(proj, "proj"), _stream()), "act_columns")
 
 
 def causal_conv(proj, x_off: int, x_bias, taps, conv_bias, conv_state, cu_q, tok_seq, seq_slot, out):

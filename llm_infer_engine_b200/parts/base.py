@@ -109,6 +109,13 @@ class Norm(Part):
         if given, receives the new h rounded to its dtype (the next product's input)."""
         raise NotImplementedError
 
+    def norm_sum(self, h: torch.Tensor, y: torch.Tensor, vector: Optional[torch.Tensor] = None,
+                 act: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """For blocks whose norm comes AFTER the residual sum: h (float32 [T, d]) = norm(alpha * h + vector (.) y) in
+        place, alpha a constant of the norm and `vector` a float32 [d] scale per channel on the branch (None = ones).
+        `act`, if given, receives the new h rounded to its dtype (the next product's input)."""
+        raise NotImplementedError
+
     def defer(self, h: torch.Tensor) -> Optional["DeferredNorm"]:
         """A promise of norm(h) for a consumer that can fold the norm into its own first kernel,
         or None when this norm (or this shape) cannot be folded."""

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops, trace
-from .base import Block, DeferredBranchAdd, ScaledDelta, call_branch, register_block
+from .base import Block, DeferredBranchAdd, ScaledDelta, call_branch, register_block, single_delta
 
 
 class PreNormBlock(Block):
@@ -211,3 +211,66 @@ class PreNormScaledMixerBlock(Block):
 
 register_block("pre_norm_scaled", PreNormScaledBlock)
 register_block("pre_norm_scaled_mixer", PreNormScaledMixerBlock)
+
+
+class PostNormScaledBlock(BranchNormBlock):
+    """h = norm(alpha h + s1 (.) mixer(h)); h = norm(alpha h + s2 (.) feed_forward(h)): the norm comes AFTER the residual
+    sum, so the stream itself is what every norm returns, and the branches read the stream. alpha is a constant of the
+    norm parts (`residual_scale`), s a learned scale per channel (the roles `mixer_scale` and `feed_forward_scale`,
+    pointwise parts of kind "layer_scale"). Scale, sum and norm are one kernel (`Norm.norm_sum`), which also writes the
+    copy of the new stream that a bfloat16 engine's next product reads; the stream stays float32."""
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm",
+             "mixer_scale": "pointwise", "feed_forward_scale": "pointwise"}
+    accepts_deferred_branch_add = False
+
+    def _start(self, h, pending, ctx):
+        """Whatever the layer before has left unadded goes into the stream first."""
+        if isinstance(pending, DeferredBranchAdd):
+            h, pending = pending.apply(), None
+        pending = single_delta(pending)
+        if pending is not None:
+            ops.residual_add(h, pending)
+            ctx.carry.pop("h_act", None)
+        return h
+
+    def _branch(self, h, x, y, norm, scale):
+        """Closes a branch; returns what the next branch reads."""
+        if isinstance(y, ScaledDelta):
+            y = y.materialize()
+        act = self._new_rounded(h)
+        norm.norm_sum(h, y, scale.vector, act)
+        return h if act is None else act
+
+    def forward(self, h, pending, ctx, unit, owns_cache):
+        tracing = trace.active()
+        h = self._start(h, pending, ctx)
+        if tracing:
+            trace.push(f"Attn_{ctx.entry}")
+        x = self._rounded(h, ctx)
+        x = self._branch(h, x, call_branch(self.mixer, x, ctx, unit, owns_cache), self.mixer_norm, self.mixer_scale)
+        if tracing:
+            trace.pop()
+            trace.push(f"FFN_{ctx.entry}")
+        x = self._branch(h, x, call_branch(self.feed_forward, x, ctx), self.feed_forward_norm, self.feed_forward_scale)
+        if x is not h:
+            ctx.carry["h_act"] = x
+        if tracing:
+            trace.pop()
+        return h, None
+
+
+class PostNormScaledMixerBlock(PostNormScaledBlock):
+    """The same arrangement for a layer without a feed-forward: h = norm(alpha h + s1 (.) mixer(h))."""
+    ROLES = {"mixer": "mixer", "mixer_norm": "norm", "mixer_scale": "pointwise"}
+
+    def forward(self, h, pending, ctx, unit, owns_cache):
+        h = self._start(h, pending, ctx)
+        x = self._rounded(h, ctx)
+        x = self._branch(h, x, call_branch(self.mixer, x, ctx, unit, owns_cache), self.mixer_norm, self.mixer_scale)
+        if x is not h:
+            ctx.carry["h_act"] = x
+        return h, None
+
+
+register_block("post_norm_scaled", PostNormScaledBlock)
+register_block("post_norm_scaled_mixer", PostNormScaledMixerBlock)

@@ -70,3 +70,19 @@ class Scale(Pointwise):
 
 
 register_pointwise("scale", Scale)
+
+
+class SoftCap(Pointwise):
+    """x = cap * tanh(x / cap): logits of designs that cap them (float32). params: cap (> 0)."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        self.cap = float(params["cap"])
+        if not self.cap > 0:
+            raise ValueError(f"cap must be positive, got {self.cap}")
+
+    def forward(self, x, ctx, rows=None):
+        return ops.cap_rows(x, self.cap)
+
+
+register_pointwise("softcap", SoftCap)

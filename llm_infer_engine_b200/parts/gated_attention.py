@@ -27,6 +27,11 @@ Three more options change single scores, each off by default:
                                              beyond, the last row for everything farther; added after the cap, unscaled
     sink = "learned"                         the sink's score is a learned number per head instead of 0
 
+    q_i <- q_i (1 + a ln(floor((i + 1) / n) + 1))    `q_temp` {coef a, every n}: a temperature on the queries that grows
+                                             with the position i, applied after the query norm (float32)
+    gate = "head"                            ONE gate per head instead of one per channel: Wg has H rows and head h's
+                                             output is multiplied by sigmoid(g_i)_h
+
 Two more, also off by default: `position` (a position encoding, e.g. rotary: q and k are encoded before the scores and
 keys are cached encoded; it takes the place of the query/key norm) and `weights = "sigmoid"`: no softmax, a visible
 key's weight is sigmoid(s_ij + b_head) with a learned number per head, and nothing is normalised over the keys.
@@ -68,7 +73,8 @@ def distance_buckets(rows: int, far: float, longest: int) -> List[int]:
 
 class GatedAttention(Mixer):
     """params: hidden, n_heads, n_kv_heads, head_dim, v_head_dim, scale (None = 1/sqrt(head_dim)), window (0 = every
-    earlier key), keep_first, sink (bool), qk_norm_eps (None = no query/key norm), gate (bool), value_blend
+    earlier key), keep_first, sink (bool), qk_norm_eps (None = no query/key norm), gate (bool, or "head" for one gate
+    per head), q_temp (None or {coef, every}), value_blend
     (None, "first": leaves its projected values for later layers, or "blend": mixes them into its own),
     blend_key (name under which the first layer's values travel through the step), names (overrides of the
     tensors' checkpoint sub-names), position (PartSpec of a position encoding for q and k, None = none), weights
@@ -109,6 +115,13 @@ class GatedAttention(Mixer):
         if self.sigmoid and (p.get("sink") or self.softcap or self.distance_bias is not None or self.keep_first):
             raise ValueError("sigmoid weights go with scale and window only")
         self.gate = bool(p.get("gate", False))
+        self.head_gate = p.get("gate") == "head"
+        temp = p.get("q_temp")
+        self.temp_coef, self.temp_every = (float(temp["coef"]), int(temp["every"])) if temp else (0.0, 0)
+        if temp and self.temp_every <= 0:
+            raise ValueError(f"q_temp.every must be positive, got {self.temp_every}")
+        if temp and self.position is not None:
+            raise ValueError("a query temperature goes with the query/key norm's kernel, not with a position encoding")
         self.value_blend = p.get("value_blend")
         if self.value_blend not in (None, "first", "blend"):
             raise ValueError(f"value_blend must be None, 'first' or 'blend', got {self.value_blend!r}")
@@ -125,7 +138,7 @@ class GatedAttention(Mixer):
         specs = {n["q"]: ParamSpec((self.nq, d)), n["k"]: ParamSpec((self.nk, d)), n["v"]: ParamSpec((self.nv, d)),
                  n["o"]: ParamSpec((d, self.no))}
         if self.gate:
-            specs[n["gate"]] = ParamSpec((self.no, d))
+            specs[n["gate"]] = ParamSpec((self.n_heads if self.head_gate else self.no, d))
         if self.qk_norm_eps is not None:
             specs[n["q_norm"]] = ParamSpec((self.nq,), role="vector", init=("ones",))
             specs[n["k_norm"]] = ParamSpec((self.nk,), role="vector", init=("ones",))
@@ -209,12 +222,16 @@ class GatedAttention(Mixer):
             q = torch.empty((T, self.nq), dtype=proj.dtype, device=proj.device)
             ops.qk_norm_store(proj, q, kv.k, kv.v, self.q_w, self.k_w, float(self.qk_norm_eps or 0.0), ctx.tok_pos,
                               ctx.tok_seq, ctx.seq_slot, kv.block_table, kv.page_size, self.n_heads, self.n_kv_heads,
-                              self.head_dim, self.v_head_dim, owns_cache, lam=self.lam, v_first=v_first)
+                              self.head_dim, self.v_head_dim, owns_cache, lam=self.lam, v_first=v_first,
+                              temp_coef=self.temp_coef, temp_every=self.temp_every)
         trace.pop()
         out = torch.empty((T, self.no), dtype=proj.dtype, device=proj.device)
         gate = proj[:, self.nq + self.nk + self.nv:] if self.gate else None
         trace.push("FlashDecode" if ctx.decode else "FlashAttn")
-        ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.options, gate=gate)
+        ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.options,
+                      gate=None if self.head_gate else gate)
+        if self.head_gate:
+            ops.sigmoid_gate(out, gate, group=self.v_head_dim)
         trace.pop()
         trace.push("Output_proj")
         y = self.o(out, out_dtype=torch.float32)

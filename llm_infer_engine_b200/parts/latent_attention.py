@@ -13,6 +13,12 @@ With u [T, d] the branch input, H heads, per head `dim` plain and `rot` rotated 
     o          = concat_h(sum_j p_ij v_h,j) * sigmoid(u Wg^T)             optional output gate
     y          = o Wo^T
 
+Options, each off by default: `q_rank` r: the queries pass through a latent of their own, c_q = RMSnorm(u Wdq^T) w_q
+(float32, eps of the layer), q = c_q Wuq^T; `rot_scaling` {factor, original, fast, slow}: YaRN's blend of the rotary
+frequencies and its factor on cos and sin (`rope.yarn_frequencies`; the score scale stays as given); `window` n: token
+i sees j with 0 <= i - j < n, and the cache gives pages back behind the window; `sink` "learned": the softmax's
+denominator holds one more term exp(s_h) with a learned number per head (no key, no value, unscaled).
+
 The cache holds one row [c | k_rot] per token, and the attention kernel runs on those rows directly: since
 q_plain . (Uk_h c) = (Uk_h^T q_plain) . c, the queries become [Uk_h^T q_plain | q_rot] against ONE key head of size
 rank + rot, the latent is its own value (the first `rank` columns of the same rows, `KVRequest.values_in_keys`), and
@@ -29,23 +35,31 @@ from ..cache.cache import KVRequest
 from ..kernels import ops, trace
 from .base import AttentionOptions, Mixer, ParamSpec, register_mixer
 from .linear import Linear
+from .rope import yarn_frequencies
 
-_DEFAULT_NAMES = {"q": "q", "dkv": "dkv", "latent_norm": "dkv.norm", "uk": "uk", "uv": "uv", "gate": "g", "o": "o"}
+_DEFAULT_NAMES = {"q": "q", "dkv": "dkv", "latent_norm": "dkv.norm", "uk": "uk", "uv": "uv", "gate": "g", "o": "o",
+                  "dq": "dq", "q_norm": "dq.norm", "uq": "uq", "sink": "sink"}
 
 
-def rotation_table(rot_dims: int, base: float, positions: int, device) -> torch.Tensor:
+def rotation_table(rot_dims: int, base: float, positions: int, device, scaling=None) -> torch.Tensor:
     """float32 [positions, rot_dims / 2, 2] of (cos, sin) of position * base^(-2i / rot_dims); the angles are formed
-    in double precision and rounded once."""
+    in double precision and rounded once. `scaling` {factor, original, fast, slow}: YaRN's frequencies and factor."""
     i = torch.arange(rot_dims // 2, dtype=torch.float64)
     freq = torch.tensor(float(base), dtype=torch.float64) ** (-2.0 * i / rot_dims)
+    magnitude = 1.0
+    if scaling is not None:
+        freq, magnitude = yarn_frequencies(rot_dims, base, float(scaling["factor"]), float(scaling["original"]),
+                                           float(scaling["fast"]), float(scaling["slow"]))
     angle = torch.arange(positions, dtype=torch.float64)[:, None] * freq[None, :]
-    return torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).to(torch.float32).contiguous().to(device)
+    table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1) * magnitude
+    return table.to(torch.float32).contiguous().to(device)
 
 
 class LatentAttention(Mixer):
     """params: hidden, n_heads, head_dim (plain part), rot_dim, v_head_dim, kv_rank, scale, rot_base, rot_dims (how many
     of the rot_dim entries are rotated; default all), norm_eps, gate (bool), owns_latent (bool: False = reads an
-    earlier layer's latent), out_float32 (bool), names."""
+    earlier layer's latent), out_float32 (bool), names; q_rank (None = queries straight from the input), rot_scaling
+    (None or {factor, original, fast, slow}), window (0 = every earlier token), sink (None or "learned")."""
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
@@ -62,20 +76,36 @@ class LatentAttention(Mixer):
         self.owns_latent = bool(p.get("owns_latent", True))
         self.out_float32 = bool(p.get("out_float32", False))
         self.names = dict(_DEFAULT_NAMES, **(p.get("names") or {}))
-        self.options = AttentionOptions(scale=float(p["scale"]))
+        self.q_rank = int(p["q_rank"]) if p.get("q_rank") else 0
+        self.rot_scaling = dict(p["rot_scaling"]) if p.get("rot_scaling") else None
+        self.window = int(p.get("window") or 0)
+        if p.get("sink") not in (None, False, "learned"):
+            raise ValueError(f"sink must be None or 'learned', got {p.get('sink')!r}")
+        self.learned_sink = p.get("sink") == "learned"
+        self.options = AttentionOptions(scale=float(p["scale"]), window=self.window)
         self.nq = self.n_heads * (self.dim + self.rot)
         self.no = self.n_heads * self.vdim
         self.row = self.rank + self.rot
-        self.table = rotation_table(max(self.rot_dims, 2), self.rot_base, runtime.max_positions, runtime.device) \
-            if runtime.device.type == "cuda" else None
+        self.table = rotation_table(max(self.rot_dims, 2), self.rot_base, runtime.max_positions, runtime.device,
+                                    self.rot_scaling) if runtime.device.type == "cuda" else None
+        self.uq: Linear = None
+        self.q_norm_w = None
         self.proj: Linear = None
         self.o: Linear = None
         self.norm_w = self.uk_t = self.uv = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         n, d = self.names, self.hidden
-        specs = {n["q"]: ParamSpec((self.nq, d)), n["uk"]: ParamSpec((self.n_heads * self.dim, self.rank)),
+        specs = {n["uk"]: ParamSpec((self.n_heads * self.dim, self.rank)),
                  n["uv"]: ParamSpec((self.no, self.rank)), n["o"]: ParamSpec((d, self.no))}
+        if self.q_rank:
+            specs[n["dq"]] = ParamSpec((self.q_rank, d))
+            specs[n["q_norm"]] = ParamSpec((self.q_rank,), role="vector", init=("ones",))
+            specs[n["uq"]] = ParamSpec((self.nq, self.q_rank))
+        else:
+            specs[n["q"]] = ParamSpec((self.nq, d))
+        if self.learned_sink:
+            specs[n["sink"]] = ParamSpec((self.n_heads,), role="vector", init=("uniform", -1.0, 1.0))
         if self.owns_latent:
             specs[n["dkv"]] = ParamSpec((self.row, d))
             specs[n["latent_norm"]] = ParamSpec((self.rank,), role="vector", init=("ones",))
@@ -85,9 +115,18 @@ class LatentAttention(Mixer):
 
     def load(self, tensors):
         n = self.names
-        ws = [tensors[n["q"]]] + ([tensors[n["dkv"]]] if self.owns_latent else []) + ([tensors[n["gate"]]] if self.gate else [])
+        ws = [tensors[n["dq"] if self.q_rank else n["q"]]] + ([tensors[n["dkv"]]] if self.owns_latent else []) + \
+            ([tensors[n["gate"]]] if self.gate else [])
         dtype = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
-        self.proj = Linear(torch.cat([w.to(dtype) for w in ws], dim=0))          # rows: q | latent | gate
+        self.proj = Linear(torch.cat([w.to(dtype) for w in ws], dim=0))          # rows: q (or its latent) | latent | gate
+        self.q_cols = self.q_rank or self.nq                                     # columns the first part takes
+        if self.q_rank:
+            self.uq = Linear(tensors[n["uq"]])
+            self.q_norm_w = tensors[n["q_norm"]].to(torch.float32).contiguous()
+        if self.learned_sink:
+            import dataclasses
+            self.options = dataclasses.replace(self.options,
+                                               sink_values=tensors[n["sink"]].to(torch.float32).contiguous())
         self.o = Linear(tensors[n["o"]])
         # per head: Uk^T as [rank, dim] (the product q_plain -> latent space), Uv as [vdim, rank]
         self.uk_t = tensors[n["uk"]].to(dtype).view(self.n_heads, self.dim, self.rank).transpose(1, 2).contiguous()
@@ -96,10 +135,11 @@ class LatentAttention(Mixer):
             self.norm_w = tensors[n["latent_norm"]].to(torch.float32).contiguous()
 
     def weight_bytes(self) -> int:
-        return self.proj.nbytes() + self.o.nbytes() + (self.uk_t.numel() + self.uv.numel()) * self.uk_t.element_size()
+        return self.proj.nbytes() + self.o.nbytes() + (self.uk_t.numel() + self.uv.numel()) * self.uk_t.element_size() \
+            + (self.uq.nbytes() if self.uq is not None else 0)
 
     def cache_requests(self):
-        return [KVRequest(1, self.row, 0, values_in_keys=self.rank)]
+        return [KVRequest(1, self.row, self.window, values_in_keys=self.rank)]
 
     def forward(self, x, ctx, unit, owns_cache, residual=None):
         if owns_cache != self.owns_latent:
@@ -112,11 +152,17 @@ class LatentAttention(Mixer):
         trace.pop()
         trace.push("Latent+KV_cache")
         q = torch.empty((T, H * self.row), dtype=proj.dtype, device=proj.device)
-        ops.latent_prepare(proj, 0, self.nq, q, kv.k, self.norm_w, self.eps, self.table, self.rot_dims, ctx.tok_pos,
+        q_src = None
+        if self.q_rank:
+            # the queries' own latent: norm of its columns (float32), then the second product
+            cq = ops.rmsnorm_cols(proj, 0, self.q_rank, self.q_norm_w, self.eps,
+                                  torch.empty((T, self.q_rank), dtype=proj.dtype, device=proj.device))
+            q_src = self.uq(cq)
+        ops.latent_prepare(proj, 0, self.q_cols, q, kv.k, self.norm_w, self.eps, self.table, self.rot_dims, ctx.tok_pos,
                            ctx.tok_seq, ctx.seq_slot, kv.block_table, kv.page_size, H, self.dim, self.rot, self.rank,
-                           owns_cache)
+                           owns_cache, q_src=q_src)
         # the plain query parts into the latent's space: q[:, h, :rank] = q_plain[:, h] Uk_h
-        ops.batched_gemm_nt(proj, self.uk_t, q, self.dim + self.rot, self.row, self.dim)
+        ops.batched_gemm_nt(proj if q_src is None else q_src, self.uk_t, q, self.dim + self.rot, self.row, self.dim)
         trace.pop()
         lat = torch.empty((T, H * self.rank), dtype=proj.dtype, device=proj.device)
         trace.push("FlashDecode" if ctx.decode else "FlashAttn")
@@ -126,7 +172,7 @@ class LatentAttention(Mixer):
         out = torch.empty((T, self.no), dtype=proj.dtype, device=proj.device)
         ops.batched_gemm_nt(lat, self.uv, out, self.rank, self.vdim, self.rank)
         if self.gate:
-            ops.sigmoid_gate(out, proj[:, self.nq + (self.row if self.owns_latent else 0):])
+            ops.sigmoid_gate(out, proj[:, self.q_cols + (self.row if self.owns_latent else 0):])
         y = self.o(out, out_dtype=torch.float32) if self.out_float32 else self.o(out)
         trace.pop()
         return y

@@ -15,6 +15,10 @@ of the choices, in float32. A token's result does not depend on what else is in 
 Options: `gated` False makes an expert down_e(act(up_e u)), one product in front of the activation. `scoring`
 "softmax_all" is a second rule for the router: s = softmax(z) over ALL its outputs, the `top` largest of s + c are chosen
 (c a stored correction that steers the choice only), and a_t,e = s_t,e / (sum of the chosen s + 1e-20) * `weight_scale`.
+"sigmoid" is a third: s = sigmoid(z) one by one, the `top` largest choose and weigh as they are (times `weight_scale`),
+not normalised. `weight_on` "input" (default "output"): the weight multiplies what the expert READS, y_t = sum over e of
+expert_e(a_t,e u_t), which is not the same thing under a non-linear expert; the rows are scaled while they are gathered
+into the order of their experts, and the combine adds with weight one.
 `identity_experts` n: the router has n more outputs than there are experts; the last n stand for experts that return
 their input (their share is weight * u_t), and they hold no tensors. Prompts of a bfloat16 engine
 hand the two products to the vendor library's grouped GEMM instead (as the dense layers hand theirs to its plain one):
@@ -34,8 +38,8 @@ from ..config.spec import PartSpec
 class RoutedExperts(FeedForward):
     """params: hidden, n_experts, top, expert_ff, activation (default "silu"), router_bias (bool, default True),
     shared_ff (width of the shared expert, None = none), shared_activation (default: `activation`), gated (default
-    True), scoring ("softmax_top", the default, or "softmax_all"), weight_scale (default 1), identity_experts (default
-    0), names (checkpoint sub-names: router, router_bias, correction, expert (a pattern with {e}), gate, up, down,
+    True), scoring ("softmax_top", the default, "softmax_all" or "sigmoid"), weight_scale (default 1), weight_on
+    ("output", the default, or "input"), identity_experts (default 0), names (checkpoint sub-names: router, router_bias, correction, expert (a pattern with {e}), gate, up, down,
     shared)."""
 
     def __init__(self, params, runtime):
@@ -52,8 +56,15 @@ class RoutedExperts(FeedForward):
         self.router_bias = bool(p.get("router_bias", True))
         self.gated = bool(p.get("gated", True))
         self.scoring = str(p.get("scoring", "softmax_top"))
-        if self.scoring not in ("softmax_top", "softmax_all"):
-            raise ValueError(f"scoring must be 'softmax_top' or 'softmax_all', got {self.scoring!r}")
+        if self.scoring not in ("softmax_top", "softmax_all", "sigmoid"):
+            raise ValueError(f"scoring must be 'softmax_top', 'softmax_all' or 'sigmoid', got {self.scoring!r}")
+        self.route_mode = {"softmax_top": ops.ROUTE_SOFTMAX_TOP, "softmax_all": ops.ROUTE_SOFTMAX_ALL,
+                           "sigmoid": ops.ROUTE_SIGMOID}[self.scoring]
+        self.weight_on_input = str(p.get("weight_on", "output")) == "input"
+        if p.get("weight_on", "output") not in ("output", "input"):
+            raise ValueError(f"weight_on must be 'output' or 'input', got {p.get('weight_on')!r}")
+        if self.weight_on_input and int(p.get("identity_experts") or 0):
+            raise ValueError("weights on the experts' input do not go with experts that return their input")
         self.weight_scale = float(p.get("weight_scale", 1.0))
         self.n_identity = int(p.get("identity_experts") or 0)
         self.n_outputs = self.n_experts + self.n_identity          # what the router has outputs for
@@ -123,7 +134,7 @@ class RoutedExperts(FeedForward):
             xin = x if x.dtype == w.dtype else x.to(w.dtype)
             ids = torch.empty((T, top), dtype=torch.int32, device=dev)
             weights = torch.empty((T, top), dtype=torch.float32, device=dev)
-            ops.moe_route(x, self.w_router, self.b_router, ids, weights, self.scoring == "softmax_all", self.correction,
+            ops.moe_route(x, self.w_router, self.b_router, ids, weights, self.route_mode, self.correction,
                           self.weight_scale)
             n_pairs = T * top
             small = n_pairs <= ops.GROUPED_SMALL_ROWS
@@ -138,8 +149,11 @@ class RoutedExperts(FeedForward):
                 extra = torch.empty(E + n_pairs, dtype=torch.int32, device=dev)
                 group_end, pair_pos = extra[:E], extra[E:]
                 ops.moe_sort(ids, E, tile, sorted_token, sorted_pair, tile_group, group_end, pair_pos)
-                xs = ops.moe_gather_rows(xin, sorted_token, torch.empty((n_tiles * tile, self.hidden), dtype=w.dtype,
-                                                                         device=dev))
+                xs = torch.empty((n_tiles * tile, self.hidden), dtype=w.dtype, device=dev)
+                if self.weight_on_input:
+                    ops.moe_gather_scaled(x, sorted_token, sorted_pair, weights, xs)
+                else:
+                    ops.moe_gather_rows(xin, sorted_token, xs)
                 try:
                     gu = ops.library_grouped_mm(xs, w, group_end)
                 except RuntimeError as exc:
@@ -160,8 +174,15 @@ class RoutedExperts(FeedForward):
             ops.moe_sort(ids, E, tile, sorted_token, sorted_pair, tile_group)
             # gate and up of every pair's expert with the activation; rows stay in sorted order
             act = torch.empty((n_tiles * tile, self.expert_ff), dtype=w.dtype, device=dev)
-            ops.routed_gemm_nt(xin, sorted_token, w, act, None, tile_group, n_tiles * tile, small, dual=self.gated,
-                               act=self.activation)
+            if self.weight_on_input:
+                # every pair's row times its weight, already in sorted order (padding rows are zeros)
+                xs = ops.moe_gather_scaled(x, sorted_token, sorted_pair, weights,
+                                           torch.empty((n_tiles * tile, self.hidden), dtype=w.dtype, device=dev))
+                ops.routed_gemm_nt(xs, None, w, act, None, tile_group, n_tiles * tile, small, dual=self.gated,
+                                   act=self.activation)
+            else:
+                ops.routed_gemm_nt(xin, sorted_token, w, act, None, tile_group, n_tiles * tile, small, dual=self.gated,
+                                   act=self.activation)
             # down: back to the order of the pairs, float32
             y = torch.empty((n_pairs, self.hidden), dtype=torch.float32, device=dev)
             ops.routed_gemm_nt(act, None, self.w_down, y, sorted_pair, tile_group, n_tiles * tile, small)
@@ -175,7 +196,7 @@ class RoutedExperts(FeedForward):
         out = torch.empty((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         if not self.n_identity:
-            return ops.moe_combine(y, weights, shared, out, pair_pos)
+            return ops.moe_combine(y, self.top if self.weight_on_input else weights, shared, out, pair_pos)
         ops.moe_combine_identity(y, weights, ids, self.n_experts, x, out, pair_pos)
         if shared is not None:
             ops.residual_add(out, shared)

@@ -17,7 +17,8 @@ from .base import DeferredNorm, Norm, ParamSpec, ScaledDelta, register_norm, sin
 class RMSNorm(Norm):
     """params: size (width of a row), eps; weight_name (the tensor's name under the part's checkpoint name,
     default "weight"; "" = the part's name itself); weight_offset (default 0: the norm multiplies by
-    weight_offset + the stored tensor, for checkpoints that store the weight around zero)."""
+    weight_offset + the stored tensor, for checkpoints that store the weight around zero); residual_scale (default 1:
+    the constant alpha of `norm_sum`, the form for blocks whose norm comes AFTER the residual sum)."""
 
     kind = "rmsnorm"
 
@@ -27,6 +28,7 @@ class RMSNorm(Norm):
         self.eps = float(params["eps"])
         self.weight_name = str(params.get("weight_name", "weight"))
         self.weight_offset = float(params.get("weight_offset", 0.0))
+        self.residual_scale = float(params.get("residual_scale", 1.0))
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -73,6 +75,12 @@ class RMSNorm(Norm):
     def add_normed(self, h, y, bias=None, act=None):
         trace.push("RMSNorm")
         ops.branch_norm_add(h, y, bias, self.weight, self.eps, act)
+        trace.pop()
+        return h
+
+    def norm_sum(self, h, y, vector=None, act=None):
+        trace.push("RMSNorm")
+        ops.scaled_sum_norm(h, y, vector, self.residual_scale, self.weight, self.eps, act)
         trace.pop()
         return h
 

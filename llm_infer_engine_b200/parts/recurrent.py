@@ -21,6 +21,14 @@ output gate. With C channels in `blocks` equal groups and K taps:
     S_t = a_t S_(t-1) + sqrt(1 - a_t^2) (i_t c_t)                    S [C] from zero, the first token like any other
     out = (S (.) y) Wo^T
 
+`decayed_linear_attention` — linear attention with a constant decay per head ("lightning" attention). With H heads,
+D query/key channels and Dv value channels a head, and an activation act on all three projections:
+
+    q = act(u Wq^T), k = act(u Wk^T), v = act(u Wv^T)
+    S_t = a_h S_(t-1) + k_t v_t^T                    per head, S [D, Dv] from zero; a_h a constant of the model
+    o_t = S_t^T q_t                                  read from the NEW state, no other scale
+    y   = (concat_h(o_t) / sqrt(mean(concat_h(o_t)^2) + eps) * w) (.) sigmoid(u Wg^T) Wo^T     ONE norm over all heads
+
 The state is S and the last K-1 inputs x of the convolution. Gates, decays, their logarithms and exponentials, the
 state and the norm of what is read are float32 in both engines; the projections have the activation type.
 """
@@ -185,3 +193,77 @@ class GatedRecurrentUnit(Mixer):
 
 
 register_mixer("gated_recurrent_unit", GatedRecurrentUnit)
+
+
+class DecayedLinearAttention(Mixer):
+    """params: hidden, n_heads, dim (query/key channels a head), v_dim (value channels a head), decay (a list of n_heads
+    constants), activation (of q, k and v; default "silu"), norm_eps, names (overrides of the checkpoint sub-names q, k,
+    v, gate, norm, o)."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        p = params
+        self.hidden, self.n_heads = int(p["hidden"]), int(p["n_heads"])
+        self.dim, self.v_dim = int(p["dim"]), int(p["v_dim"])
+        if self.dim > 512:
+            raise ValueError(f"dim ({self.dim}) exceeds what the scan kernel takes (512)")
+        decay = [float(a) for a in p["decay"]]
+        if len(decay) != self.n_heads:
+            raise ValueError(f"decay holds {len(decay)} constants for {self.n_heads} heads")
+        name = str(p.get("activation", "silu"))
+        if name not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {name!r} is not known ({sorted(ops.ACTIVATIONS)})")
+        self.activation = ops.ACTIVATIONS[name]
+        self.eps = float(p["norm_eps"])
+        self.names = dict({"q": "q", "k": "k", "v": "v", "gate": "g", "norm": "norm", "o": "o"}, **(p.get("names") or {}))
+        self.nq, self.nv = self.n_heads * self.dim, self.n_heads * self.v_dim
+        # the constants as float32: rounded once from the configuration's double-precision numbers
+        self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(runtime.device)
+        self.proj: Linear = None
+        self.o: Linear = None
+        self.norm_w = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n, d = self.names, self.hidden
+        return {n["q"]: ParamSpec((self.nq, d)), n["k"]: ParamSpec((self.nq, d)), n["v"]: ParamSpec((self.nv, d)),
+                n["gate"]: ParamSpec((self.nv, d)),
+                n["norm"]: ParamSpec((self.nv,), role="vector", init=("ones",)),
+                n["o"]: ParamSpec((d, self.nv))}
+
+    def load(self, tensors):
+        n = self.names
+        ws = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]], tensors[n["gate"]]]
+        dtype = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.proj = Linear(torch.cat([w.to(dtype) for w in ws], dim=0))         # [q | k | v | gate]
+        self.o = Linear(tensors[n["o"]])
+        self.norm_w = tensors[n["norm"]].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.proj.nbytes() + self.o.nbytes() + 4 * self.nv
+
+    def cache_requests(self):
+        return [StateRequest("S", (self.n_heads, self.dim, self.v_dim))]
+
+    def forward(self, x, ctx, unit, owns_cache):
+        T, dev = x.shape[0], x.device
+        trace.push("QKV_proj")
+        proj = self.proj(x)                                            # [T, q | k | v | gate]
+        trace.pop()
+        trace.push("Recurrence")
+        q = torch.empty((T, self.nq), dtype=torch.float32, device=dev)
+        k = torch.empty((T, self.nq), dtype=torch.float32, device=dev)
+        v = torch.empty((T, self.nv), dtype=torch.float32, device=dev)
+        ops.act_columns(proj, [(0, q), (self.nq, k), (2 * self.nq, v)], self.activation)
+        read = torch.empty((T, self.nv), dtype=torch.float32, device=dev)
+        ops.matrix_scan(q, k, v, unit.state["S"], ctx.cu_q, ctx.seq_slot, read, ctx.n_seqs, self.n_heads, self.dim,
+                        self.v_dim, write_state=owns_cache, max_len=ctx.max_q_len, head_decay=self.decay)
+        normed = torch.empty((T, self.nv), dtype=proj.dtype, device=dev)
+        ops.head_rmsnorm(read, self.norm_w, self.eps, normed, self.nv, gate=proj[:, 2 * self.nq + self.nv:])
+        trace.pop()
+        trace.push("Output_proj")
+        y = self.o(normed, out_dtype=torch.float32)
+        trace.pop()
+        return y
+
+
+register_mixer("decayed_linear_attention", DecayedLinearAttention)

@@ -41,6 +41,26 @@ def inverse_frequencies(rot_dim: int, theta: float, scaling: Optional[dict]) -> 
     return torch.where(medium, blended, scaled)
 
 
+def yarn_frequencies(dims: int, base: float, factor: float, original: float, fast: float, slow: float):
+    """YaRN's blend of rotary frequencies, in double precision: float64 [dims / 2] and the factor on cos and sin.
+
+    With f_i = base^(-2i/dims) and where(t) = dims ln(original / (2 pi t)) / (2 ln base) (the pair whose wave turns t
+    times within `original` positions), lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1): pairs below lo keep f_i, pairs above hi get f_i / factor, and
+    those between are blended, f_i / factor * ramp_i + f_i (1 - ramp_i). cos and sin are multiplied by
+    0.1 ln(factor) + 1."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = torch.tensor(float(base), dtype=torch.float64) ** (-2.0 * i / dims)
+
+    def where(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(where(fast)), 0)
+    hi = min(math.ceil(where(slow)), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
 class RotaryEncoding(PositionEncoding):
     """params: rot_dim (how many leading elements of a head are rotated), theta, scaling
     (None or {"rope_type": "llama3", factor, low_freq_factor, high_freq_factor,
