@@ -146,13 +146,18 @@ def expert(x, w, pre):
     return (silu(x @ w[pre + "gate"].T) * (x @ w[pre + "up"].T)) @ w[pre + "down"].T
 
 
-def routed_experts(h, f, w, pre):
+def routed_experts(h, f, w, pre, margins_out=None):
     """Sigmoid router: the `top` largest scores choose, the scores themselves weigh, and the weight multiplies what
-    the expert READS. A shared expert reads every token as it is."""
+    the expert READS. A shared expert reads every token as it is. `margins_out`, a list, receives per token the gap
+    between the last chosen logit and the first one left out (infinite when every expert is chosen)."""
     T = h.shape[0]
-    scores = torch.sigmoid(h @ w[pre + "router"].T)
+    z = h @ w[pre + "router"].T
+    scores = torch.sigmoid(z)
     top = f["router"]["top"]
     val, idx = torch.topk(scores, top, dim=-1)
+    if margins_out is not None:
+        zs = torch.sort(z, dim=-1, descending=True).values
+        margins_out.append(zs[:, top - 1] - zs[:, top] if top < z.shape[1] else torch.full((T,), float("inf")))
     out = torch.zeros_like(h)
     for t in range(T):
         for c in range(top):
@@ -167,8 +172,9 @@ def routed_experts(h, f, w, pre):
 MIXERS = {"attention": attention, "latent_attention": latent_attention, "lightning": lightning}
 
 
-def forward(cfg, w, tokens, layers_out=None):
-    """Logits [T, vocab] of one whole sequence. `layers_out`, a list, receives the stream after every layer."""
+def forward(cfg, w, tokens, layers_out=None, margins_out=None):
+    """Logits [T, vocab] of one whole sequence. `layers_out`, a list, receives the stream after every layer;
+    `margins_out`, a list, every router's choice margins per token."""
     eps, alpha = cfg["norm"]["eps"], cfg["postln_alpha"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     for i, layer in enumerate(cfg["layers"]):
@@ -176,7 +182,7 @@ def forward(cfg, w, tokens, layers_out=None):
         y = MIXERS[layer["type"]](x, layer["mixer"], w, pre + "mix.", eps)
         x = rms(alpha * x + y * w[pre + "ls1"], eps) * w[pre + "norm1"]
         if layer.get("mlp") is not None:
-            y = routed_experts(x, layer["mlp"], w, pre + "mlp.")
+            y = routed_experts(x, layer["mlp"], w, pre + "mlp.", margins_out)
             x = rms(alpha * x + y * w[pre + "ls2"], eps) * w[pre + "norm2"]
         if layers_out is not None:
             layers_out.append(x.clone())
