@@ -452,6 +452,32 @@ def ganupel_config(width: int, heads: int, kv_heads: int, head_dim: int, ff: int
     return {"architecture": "Ganupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers}
 
 
+def burinex_config(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab: int, n_layers: int,
+                   window: int) -> dict:
+    """A Burinex configuration with a Llama shape's layer sizes. Layers cycle through four kinds: latent attention
+    (queries through a latent of 6 head sizes, a cached latent of 4 head sizes with a rotated part of half a head size,
+    YaRN-scaled rotation, a window, a learned sink), grouped-query attention with a query temperature, a sink and a gate
+    per head, linear attention with a decay per head (as many heads, a head size of key and of value channels), and the
+    grouped-query attention again. Every layer has the routed feed-forward: 3 of 16 experts of ff / 4 under a sigmoid
+    router whose weights multiply the experts' input, plus a shared expert of ff / 4 (the active width of the dense
+    feed-forward of the shape)."""
+    rot = head_dim // 2
+    latent = {"heads": heads, "dim": head_dim, "rot_dim": rot, "vdim": head_dim, "kv_rank": 4 * head_dim,
+              "q_rank": 6 * head_dim, "scale": (head_dim + rot) ** -0.5, "mask": {"size": window} if window else None,
+              "rot": {"base": 10000.0, "dims": rot,
+                      "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+            "q_temp": {"coef": 0.3, "every": 128}}
+    linear = {"heads": heads, "dim": head_dim, "vdim": head_dim,
+              "decay": [1.0 - 2.0 ** (-1.0 - 7.0 * h / max(heads - 1, 1)) for h in range(heads)]}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 3}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4}}
+    kinds = [("latent_attention", latent), ("attention", attn), ("lightning", linear), ("attention", attn)]
+    layers = [{"type": kinds[i % 4][0], "mixer": json.loads(json.dumps(kinds[i % 4][1])), "mlp": dict(moe)}
+              for i in range(n_layers)]
+    return {"architecture": "Burinex", "vocab": vocab, "width": width, "postln_alpha": 1.0, "logit_softcap": 30.0,
+            "norm": {"eps": 1e-6}, "layers": layers}
+
+
 def step_tables(engine, pk: dict, title: str, batch: int = 8) -> str:
     """Per-kernel tables (eager steps, CUDA events) of a decode step at `batch` sequences and of a 2,048-token
     prompt."""
@@ -491,7 +517,7 @@ def step_tables(engine, pk: dict, title: str, batch: int = 8) -> str:
 
 def run_designs(args, pk: dict, which: str = "Zemivik") -> str:
     """Zemivik (or, with which="Dofipel", Dofipel with a window of 1,024) beside Llama at equal layer sizes, or, with
-    which="Ganupel", Ganupel beside Dofipel (random weights, bfloat16): decode throughput at batch 1, 8 and 64
+    which="Ganupel" or "Burinex", that design beside Dofipel (random weights, bfloat16): decode throughput at batch 1, 8 and 64
     after 512-token prompts (captured steps, device time), prefill throughput of one 2,048-token prompt, and the
     per-kernel tables of both. Zemivik once without a mask (the attention work of Llama's) and once with a window
     of 1,024 tokens that keeps the first four. The shared vocabulary is kept small so that the layers, not the
@@ -503,7 +529,7 @@ def run_designs(args, pk: dict, which: str = "Zemivik") -> str:
     vocab = 32000
     shapes = [("1B layer sizes", CONFIG_1B), ("8B layer sizes", CONFIG_8B)]
     steps = min(args.steps, 64)
-    lines = [f"{which} beside {'Dofipel' if which == 'Ganupel' else 'Llama'} at equal layer sizes, {n_layers} layers, vocabulary {vocab}, bfloat16, random weights "
+    lines = [f"{which} beside {'Dofipel' if which in ('Ganupel', 'Burinex') else 'Llama'} at equal layer sizes, {n_layers} layers, vocabulary {vocab}, bfloat16, random weights "
              f"(peaks: {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s, {pk['source']}).", "",
              "| layer sizes | design | decode b1 tok/s | ms/step | decode b8 tok/s | ms/step | decode b64 tok/s | ms/step | "
              f"prefill {PREFILL_TOKENS} tok/s | ms |", "|---|---|---|---|---|---|---|---|---|---|"]
@@ -522,6 +548,9 @@ def run_designs(args, pk: dict, which: str = "Zemivik") -> str:
         if which == "Ganupel":
             designs = [("Dofipel, window 1024", dofipel_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024)),
                        ("Ganupel, window 1024", ganupel_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024))]
+        if which == "Burinex":
+            designs = [("Dofipel, window 1024", dofipel_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024)),
+                       ("Burinex, window 1024", burinex_config(d, hq, hkv, hd, ff, vocab, n_layers, 1024))]
         for design, cfg in designs:
             folder = scratch_folder("llmie_bench_design_")
             write_random_model(cfg, folder, seed=3, std=0.02)
@@ -643,8 +672,9 @@ def run_ours(args):
             with open(args.per_kernel_out, "w", encoding="utf-8") as f:
                 f.write(text + "\n")
         return 0
-    if args.designs or args.dofipel or args.ganupel:
-        text = run_designs(args, pk, "Ganupel" if args.ganupel else "Dofipel" if args.dofipel else "Zemivik")
+    if args.designs or args.dofipel or args.ganupel or args.burinex:
+        text = run_designs(args, pk, "Burinex" if args.burinex else "Ganupel" if args.ganupel else
+                           "Dofipel" if args.dofipel else "Zemivik")
         print(text)
         if args.per_kernel_out:
             with open(args.per_kernel_out, "w", encoding="utf-8") as f:
@@ -822,6 +852,10 @@ def main():
     ap.add_argument("--ganupel", action="store_true",
                     help="the same comparison for Ganupel (sigmoid-weight attention beside a gated linear recurrence, "
                          "recurrent units, PolyNorm and routed feed-forwards) beside Dofipel, the closest design")
+    ap.add_argument("--burinex", action="store_true",
+                    help="the same comparison for Burinex (post-norm layers; latent attention with a query latent, a "
+                         "window and a learned sink; gated attention with a query temperature; linear attention with a "
+                         "decay per head; routed experts weighted on their input) beside Dofipel, the closest design")
     ap.add_argument("--heads", type=int, default=32, help="query heads of --attention-sweep")
     ap.add_argument("--kv-heads", type=int, default=8, help="KV heads of --attention-sweep")
     ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128], help="head size of --attention-sweep")
