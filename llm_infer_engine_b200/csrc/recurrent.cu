@@ -203,6 +203,41 @@ __global__ void head_rmsnorm_kernel(const float* __restrict__ o, const float* __
     y[item * Dv + i] = from_f32<T>(row[i] * r * w[i] / (1.f + expf(-to_f32(gr[i]))));
 }
 
+// The same for wide items (a token's whole row of concatenated heads): a block per item, so that a one-token step's few
+// rows are not each one warp's work. Dv % 4 == 0 and 16-byte aligned rows: four elements a thread and access.
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps, T* __restrict__ y, int Dv,
+                   const T* __restrict__ gate, int gate_ld, int items_per_row) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const size_t item = blockIdx.x;
+  const float4* row = reinterpret_cast<const float4*>(o + item * Dv);
+  const int n4 = Dv >> 2;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 x = row[i];
+    ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / (float)Dv + eps);
+  const size_t t = item / items_per_row;
+  const T* gr = gate ? gate + t * gate_ld + (item - t * items_per_row) * Dv : nullptr;
+  T* yr = y + item * Dv;
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 x = row[i];
+    const float4 wv = reinterpret_cast<const float4*>(w)[i];
+    float v[4] = {x.x * r * wv.x, x.y * r * wv.y, x.z * r * wv.z, x.w * r * wv.w};
+    if (gr) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = v[e] / (1.f + expf(-to_f32(gr[4 * i + e])));
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) yr[4 * i + e] = from_f32<T>(v[e]);
+  }
+}
+
 // Float32 copies of up to three runs of columns of proj [T, ld], each through the activation `act`:
 // out_k[t, c] = act(proj[t, off_k + c]), c < n_k. (What a linear-attention layer reads of its projections.)
 template <typename T>
@@ -606,6 +641,20 @@ extern "C" int llmie_head_rmsnorm_gated(const float* o, const float* w, float ep
                                         cudaStream_t stream) {
   if (n_items < 0 || Dv <= 0 || (gate && (items_per_row <= 0 || gate_ld < items_per_row * Dv))) return LLMIE_ERR_BAD_ARG;
   if (n_items == 0) return LLMIE_OK;
+  if (Dv >= 512 && Dv % 4 == 0 && aligned16(o) && aligned16(w) && n_items <= 0x7fffffffLL) {
+    // wide items: a block each
+    const dim3 grid((unsigned)n_items), block(Dv >= 1024 ? 256 : 128);
+    if (dtype == LLMIE_F32)
+      launch_k(row_rmsnorm_kernel<float>, grid, block, 0, stream, o, w, eps, (float*)y, Dv, (const float*)gate, gate_ld,
+               items_per_row);
+    else if (dtype == LLMIE_BF16)
+      launch_k(row_rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, stream, o, w, eps, (__nv_bfloat16*)y, Dv,
+               (const __nv_bfloat16*)gate, gate_ld, items_per_row);
+    else
+      return LLMIE_ERR_DTYPE;
+    LLMIE_LAUNCH_CHECK();
+    return LLMIE_OK;
+  }
   const int warps = 4;
   const long long blocks = (n_items + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return LLMIE_ERR_UNSUPPORTED_SIZE;

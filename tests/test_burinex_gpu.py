@@ -223,6 +223,17 @@ def test_small_kernels_of_the_design(dtype):
                            gate=gate.to(DEV)[:, 40:]).float().cpu().double()
     ref = plain.rms(read.double(), 1e-5) * wn.double() * torch.sigmoid(gate[:, 40:].double())
     assert float((got - ref).abs().max()) <= tol(dtype, float(ref.abs().max()))
+    for width in (512, 2052, 4096):                      # wide rows: a block per row
+        read_w = torch.randn(5, width, generator=g) * 4
+        w_w = torch.rand(width, generator=g) + 0.5
+        gate_w = torch.randn(5, width + 24, generator=g).to(dt)
+        for gt in (gate_w.to(DEV)[:, 24:], None):
+            got = ops.head_rmsnorm(read_w.to(DEV), w_w.to(DEV), 1e-5, torch.empty(5, width, dtype=dt, device=DEV), width,
+                                   gate=gt).float().cpu().double()
+            ref = plain.rms(read_w.double(), 1e-5) * w_w.double()
+            if gt is not None:
+                ref = ref * torch.sigmoid(gate_w[:, 24:].double())
+            assert float((got - ref).abs().max()) <= tol(dtype, float(ref.abs().max()))
     # a norm per head with a weight the heads share, and a gate
     got = ops.head_rmsnorm(read.to(DEV), wn[:20].contiguous().to(DEV), 1e-5, torch.empty(13, 60, dtype=dt, device=DEV),
                            20, gate=gate.to(DEV)[:, 40:]).float().cpu().double()
