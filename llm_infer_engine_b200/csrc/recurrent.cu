@@ -54,18 +54,21 @@ __global__ void matrix_gates_kernel(const T* __restrict__ proj, int ld, int q_of
 }
 
 constexpr int kScanThreads = 128;
-constexpr int kScanR = 16;          // state rows a thread keeps at most
+constexpr int kScanR = 16;          // state rows a thread keeps at most (one column a thread)
+constexpr int kScanRWide = 8;       // ... when it owns four columns
 
-// grid (column tiles, heads, sequences). A thread owns column j of its head's state and the rows [s R, (s+1) R) of it,
-// S = slices (a power of two up to 32, lanes that differ in their low bits), R = ceil(dim / S) <= kScanR. The next
-// token's gate, query and value are requested before the current token's products.
+// grid (column tiles, heads, sequences). A thread owns C adjacent columns (C = 1, or 4 when the value size allows) of its
+// head's state and the rows [s R, (s+1) R) of them, S = slices (a power of two up to 32, lanes that differ in their low
+// bits), R = ceil(dim / S) <= RMAX. With four columns a thread every gate, key and query entry that is loaded serves
+// four state entries: the kernel is bound by what the first-level cache delivers otherwise. The next token's gate, query
+// and values are requested before the current token's products.
 // With `head_decay` (float32 [H]) the update is S <- head_decay[h] S + k_t v_t^T with the keys k_t in the place of fg.
 // MODE 0: a sequence's whole piece, from the slot's state to the slot's state. MODE 1 and 2 work on chunk c =
 // blockIdx.z % NC of sequence blockIdx.z / NC, L tokens each, with ws float32 [n_seqs, NC, H, D, Dv] and decay float32
 // [n_seqs, NC, H, D]: MODE 1 runs a chunk that is not the sequence's last from a zero state, without outputs, and leaves
 // its end state in ws[c + 1] and the product of its gates in decay[c + 1]; MODE 2 runs a chunk from ws[c] with outputs,
 // and the last one writes the slot's state.
-template <typename T, int MODE>
+template <typename T, int MODE, int C, int RMAX>
 __global__ void __launch_bounds__(kScanThreads)
 matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, const T* __restrict__ v, int v_ld,
                    float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
@@ -79,12 +82,12 @@ matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, c
   pdl_wait();
   const int s = threadIdx.x & (S - 1);
   const int col = threadIdx.x / S;
-  const int j = blockIdx.x * (kScanThreads / S) + col;
+  const int j = (blockIdx.x * (kScanThreads / S) + col) * C;   // Dv is a multiple of C
   const int h = blockIdx.y;
   const int seq = MODE == 0 ? blockIdx.z : blockIdx.z / NC;
   const int chunk = MODE == 0 ? 0 : blockIdx.z - seq * NC;
   const bool live = j < Dv;
-  const int jj = live ? j : Dv - 1;
+  const int jj = live ? j : Dv - C;
   const int i0 = s * R;
   const int seq_end = cu_q[seq + 1];
   const int t0 = MODE == 0 ? cu_q[seq] : cu_q[seq] + chunk * L;
@@ -95,61 +98,90 @@ matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, c
   float* st = state + (((size_t)slot * H + h) * D) * Dv + jj;
   const size_t HDDv = (size_t)H * D * Dv;
   const float* start = MODE == 2 ? ws + ((size_t)seq * NC + chunk) * HDDv + ((size_t)h * D) * Dv + jj : st;
-  float St[kScanR];
+  float St[RMAX][C];
 #pragma unroll
-  for (int r = 0; r < kScanR; ++r)
-    St[r] = (MODE != 1 && r < R && i0 + r < D) ? start[(size_t)(i0 + r) * Dv] : 0.f;
-  float f[kScanR], q[kScanR], vj = 0.f;
+  for (int r = 0; r < RMAX; ++r)
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+      St[r][c] = (MODE != 1 && r < R && i0 + r < D) ? start[(size_t)(i0 + r) * Dv + c] : 0.f;
+  float f[RMAX], q[RMAX], vj[C];
   const size_t HD = (size_t)H * D;
   auto fetch = [&](int t) {
     const float* fr = fg + (size_t)t * HD + (size_t)h * D + i0;
     const float* qr = qa + (size_t)t * HD + (size_t)h * D + i0;
 #pragma unroll
-    for (int r = 0; r < kScanR; ++r) {
+    for (int r = 0; r < RMAX; ++r) {
       const bool ok = r < R && i0 + r < D;
       f[r] = ok ? fr[r] : 0.f;
       if (MODE != 1) q[r] = ok ? qr[r] : 0.f;
     }
-    vj = to_f32(v[(size_t)t * v_ld + (size_t)h * Dv + jj]);
-  };
-  float prod[kScanR];                               // MODE 1: the product of the chunk's gates
 #pragma unroll
-  for (int r = 0; r < kScanR; ++r) prod[r] = 1.f;
+    for (int c = 0; c < C; ++c) vj[c] = to_f32(v[(size_t)t * v_ld + (size_t)h * Dv + jj + c]);
+  };
+  float prod[RMAX];                                 // MODE 1: the product of the chunk's gates
+#pragma unroll
+  for (int r = 0; r < RMAX; ++r) prod[r] = 1.f;
   if (t0 < t1) fetch(t0);
   for (int t = t0; t < t1; ++t) {
-    float cf[kScanR], cq[kScanR];
-    const float cv = vj;
+    float cf[RMAX], cq[RMAX], cv[C], acc[C];
 #pragma unroll
-    for (int r = 0; r < kScanR; ++r) { cf[r] = f[r]; cq[r] = MODE != 1 ? q[r] : 0.f; }
+    for (int c = 0; c < C; ++c) { cv[c] = vj[c]; acc[c] = 0.f; }
+#pragma unroll
+    for (int r = 0; r < RMAX; ++r) { cf[r] = f[r]; cq[r] = MODE != 1 ? q[r] : 0.f; }
     if (t + 1 < t1) fetch(t + 1);
-    float acc = 0.f;
 #pragma unroll
-    for (int r = 0; r < kScanR; ++r) {
-      St[r] = keyed ? fmaf(dh, St[r], cf[r] * cv) : fmaf(cf[r], St[r], (1.f - cf[r]) * cv);
-      if (MODE == 1) prod[r] *= keyed ? dh : cf[r];
-      else acc = fmaf(St[r], cq[r], acc);
+    for (int r = 0; r < RMAX; ++r) {
+      const float gate = keyed ? dh : cf[r];
+      const float write = keyed ? cf[r] : 1.f - cf[r];
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        St[r][c] = fmaf(gate, St[r][c], write * cv[c]);
+        if (MODE != 1) acc[c] = fmaf(St[r][c], cq[r], acc[c]);
+      }
+      if (MODE == 1) prod[r] *= gate;
     }
     if (MODE != 1) {
-      for (int off = 1; off < S; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-      if (s == 0 && live) o[(size_t)t * H * Dv + (size_t)h * Dv + j] = acc;
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        for (int off = 1; off < S; off <<= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], off);
+        if (s == 0 && live) o[(size_t)t * H * Dv + (size_t)h * Dv + j + c] = acc[c];
+      }
     }
   }
   if (MODE == 1) {
     float* end = ws + ((size_t)seq * NC + chunk + 1) * HDDv + ((size_t)h * D) * Dv + jj;
     float* dec = decay + (((size_t)seq * NC + chunk + 1) * H + h) * D;
 #pragma unroll
-    for (int r = 0; r < kScanR; ++r)
+    for (int r = 0; r < RMAX; ++r)
       if (r < R && i0 + r < D) {
-        if (live) end[(size_t)(i0 + r) * Dv] = St[r];
+        if (live) {
+#pragma unroll
+          for (int c = 0; c < C; ++c) end[(size_t)(i0 + r) * Dv + c] = St[r][c];
+        }
         if (blockIdx.x == 0 && col == 0) dec[i0 + r] = prod[r];
       }
     return;
   }
   if (write_state && live && t1 >= seq_end) {
 #pragma unroll
-    for (int r = 0; r < kScanR; ++r)
-      if (r < R && i0 + r < D) st[(size_t)(i0 + r) * Dv] = St[r];
+    for (int r = 0; r < RMAX; ++r)
+      if (r < R && i0 + r < D) {
+#pragma unroll
+        for (int c = 0; c < C; ++c) st[(size_t)(i0 + r) * Dv + c] = St[r][c];
+      }
   }
+}
+
+// How a head's state is cut among threads: C columns a thread, S slices of R rows.
+struct ScanShape { int C, S, R; };
+static inline ScanShape scan_shape(int D, int Dv) {
+  ScanShape g;
+  g.C = (Dv % 4 == 0 && D <= 32 * kScanRWide) ? 4 : 1;
+  const int rmax = g.C == 4 ? kScanRWide : kScanR;
+  g.S = 1;
+  while (g.S * rmax < D) g.S <<= 1;
+  g.R = (D + g.S - 1) / g.S;
+  return g;
 }
 
 // The chain over a sequence's chunks, a thread per element of the state: ws[0] = the slot's state and
@@ -538,20 +570,22 @@ extern "C" int llmie_matrix_scan_ex(const float* qa, const float* fg, const void
   if (n_seqs < 0 || H <= 0 || D <= 0 || Dv <= 0 || v_ld < H * Dv) return LLMIE_ERR_BAD_ARG;
   if (D > 32 * kScanR) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (n_seqs == 0) return LLMIE_OK;
-  int S = 1;
-  while (S * kScanR < D) S <<= 1;
-  const int R = (D + S - 1) / S;
-  const int cols = kScanThreads / S;
+  const ScanShape g = scan_shape(D, Dv);
+  const int S = g.S, R = g.R;
+  const int cols = (kScanThreads / S) * g.C;
   const dim3 grid((Dv + cols - 1) / cols, H, n_seqs), block(kScanThreads);
   if (grid.y > 65535 || grid.z > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  if (dtype == LLMIE_F32)
-    launch_k(matrix_scan_kernel<float, 0>, grid, block, 0, stream, qa, fg, (const float*)v, v_ld, state, cu_q, seq_slot,
-             o, H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1, head_decay);
-  else if (dtype == LLMIE_BF16)
-    launch_k(matrix_scan_kernel<__nv_bfloat16, 0>, grid, block, 0, stream, qa, fg, (const __nv_bfloat16*)v, v_ld, state,
-             cu_q, seq_slot, o, H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1, head_decay);
-  else
+#define LLMIE_SCAN0(T, C, RM)                                                                                            \
+  launch_k(matrix_scan_kernel<T, 0, C, RM>, grid, block, 0, stream, qa, fg, (const T*)v, v_ld, state, cu_q, seq_slot, o, \
+           H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1, head_decay)
+  if (dtype == LLMIE_F32) {
+    if (g.C == 4) LLMIE_SCAN0(float, 4, kScanRWide); else LLMIE_SCAN0(float, 1, kScanR);
+  } else if (dtype == LLMIE_BF16) {
+    if (g.C == 4) LLMIE_SCAN0(__nv_bfloat16, 4, kScanRWide); else LLMIE_SCAN0(__nv_bfloat16, 1, kScanR);
+  } else {
     return LLMIE_ERR_DTYPE;
+  }
+#undef LLMIE_SCAN0
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -563,19 +597,19 @@ extern "C" int llmie_matrix_scan(const float* qa, const float* fg, const void* v
                               stream);
 }
 
-template <typename T>
+template <typename T, int C, int RM>
 static void matrix_scan_chunked_launch(const float* qa, const float* fg, const T* v, int v_ld, float* state,
                                        const int* cu_q, const int* seq_slot, float* o, float* ws, float* decay,
                                        int n_seqs, int H, int D, int Dv, int S, int R, int L, int NC, int write_state,
                                        const float* head_decay, cudaStream_t stream) {
-  const int cols = kScanThreads / S;
+  const int cols = (kScanThreads / S) * C;
   const dim3 grid((Dv + cols - 1) / cols, H, n_seqs * NC), block(kScanThreads);
-  launch_k(matrix_scan_kernel<T, 1>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
+  launch_k(matrix_scan_kernel<T, 1, C, RM>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
            write_state, ws, decay, L, NC, head_decay);
   const size_t HDDv = (size_t)H * D * Dv;
   launch_k(matrix_scan_chain_kernel, dim3((unsigned)((HDDv + 255) / 256), n_seqs), dim3(256), 0, stream,
            (const float*)state, cu_q, seq_slot, ws, (const float*)decay, H, D, Dv, L, NC);
-  launch_k(matrix_scan_kernel<T, 2>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
+  launch_k(matrix_scan_kernel<T, 2, C, RM>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
            write_state, ws, decay, L, NC, head_decay);
 }
 
@@ -589,18 +623,20 @@ extern "C" int llmie_matrix_scan_chunked_ex(const float* qa, const float* fg, co
     return LLMIE_ERR_BAD_ARG;
   if (D > 32 * kScanR) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (n_seqs == 0) return LLMIE_OK;
-  int S = 1;
-  while (S * kScanR < D) S <<= 1;
-  const int R = (D + S - 1) / S;
+  const ScanShape g = scan_shape(D, Dv);
+  const int S = g.S, R = g.R;
   if (H > 65535 || (long long)n_seqs * n_chunks > 65535 || n_seqs > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  if (dtype == LLMIE_F32)
-    matrix_scan_chunked_launch(qa, fg, (const float*)v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D, Dv, S,
-                               R, chunk, n_chunks, write_state, head_decay, stream);
-  else if (dtype == LLMIE_BF16)
-    matrix_scan_chunked_launch(qa, fg, (const __nv_bfloat16*)v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D,
-                               Dv, S, R, chunk, n_chunks, write_state, head_decay, stream);
-  else
+#define LLMIE_SCANC(T, C, RM)                                                                                          \
+  matrix_scan_chunked_launch<T, C, RM>(qa, fg, (const T*)v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D, Dv, \
+                                       S, R, chunk, n_chunks, write_state, head_decay, stream)
+  if (dtype == LLMIE_F32) {
+    if (g.C == 4) LLMIE_SCANC(float, 4, kScanRWide); else LLMIE_SCANC(float, 1, kScanR);
+  } else if (dtype == LLMIE_BF16) {
+    if (g.C == 4) LLMIE_SCANC(__nv_bfloat16, 4, kScanRWide); else LLMIE_SCANC(__nv_bfloat16, 1, kScanR);
+  } else {
     return LLMIE_ERR_DTYPE;
+  }
+#undef LLMIE_SCANC
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
