@@ -465,16 +465,16 @@ def burinex_config(width: int, heads: int, kv_heads: int, head_dim: int, ff: int
     latent = {"heads": heads, "dim": head_dim, "rot_dim": rot, "vdim": head_dim, "kv_rank": 4 * head_dim,
               "q_rank": 6 * head_dim, "scale": (head_dim + rot) ** -0.5, "mask": {"size": window} if window else None,
               "rot": {"base": 10000.0, "dims": rot,
-                      "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+                      "scaling": {"factor": 8.0, "original": 2048, "fast": 16.0, "slow": 2.0}}}
     attn = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
-            "q_temp": {"coef": 0.3, "every": 128}}
+            "q_temp": {"coef": 0.25, "every": 256}}
     linear = {"heads": heads, "dim": head_dim, "vdim": head_dim,
               "decay": [1.0 - 2.0 ** (-1.0 - 7.0 * h / max(heads - 1, 1)) for h in range(heads)]}
     moe = {"kind": "moe", "router": {"experts": 16, "top": 3}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4}}
     kinds = [("latent_attention", latent), ("attention", attn), ("lightning", linear), ("attention", attn)]
     layers = [{"type": kinds[i % 4][0], "mixer": json.loads(json.dumps(kinds[i % 4][1])), "mlp": dict(moe)}
               for i in range(n_layers)]
-    return {"architecture": "Burinex", "vocab": vocab, "width": width, "postln_alpha": 1.0, "logit_softcap": 30.0,
+    return {"architecture": "Burinex", "vocab": vocab, "width": width, "postln_alpha": 2.0, "logit_softcap": 50.0,
             "norm": {"eps": 1e-6}, "layers": layers}
 
 

@@ -62,7 +62,7 @@ TINY_B = {"architecture": "Burinex", "vocab": 97, "width": 100, "postln_alpha": 
 TINY_C = {"architecture": "Burinex", "vocab": 160, "width": 128, "postln_alpha": 4.0, "logit_softcap": 50.0,
           "norm": {"eps": 1e-6}, "layers": [
     {"type": "attention", "mixer": _attn(4, 2, 64, 64, 0.125, (0.25, 64)), "mlp": _moe(4, 2, 64, 64)},
-    {"type": "latent_attention", "mixer": _latent(4, 64, 16, 64, 112, 64, 0.11, 100, 10000.0, 16, (4.0, 128, 32.0, 1.0)),
+    {"type": "latent_attention", "mixer": _latent(4, 64, 16, 64, 112, 64, 0.11, 100, 20000.0, 16, (3.0, 128, 16.0, 1.0)),
      "mlp": _moe(8, 2, 32, 48)},
     {"type": "lightning", "mixer": {"heads": 2, "dim": 128, "vdim": 64, "decay": [0.9, 0.999]}, "mlp": _moe(4, 1, 64, None)},
     {"type": "attention", "mixer": _attn(2, 1, 128, 128, 0.09, (0.5, 100)), "mlp": None},
@@ -206,8 +206,8 @@ def test_small_kernels_of_the_design(dtype):
     assert float((got - ref).abs().max()) <= tol(dtype, float(ref.abs().max()))
 
     x = torch.randn(5, 301, generator=g) * 40
-    got = ops.cap_rows(x.clone().to(DEV), 30.0).cpu().double()
-    assert float((got - 30.0 * torch.tanh(x.double() / 30.0)).abs().max()) <= 1e-4
+    got = ops.cap_rows(x.clone().to(DEV), 25.0).cpu().double()
+    assert float((got - 25.0 * torch.tanh(x.double() / 25.0)).abs().max()) <= 1e-4
 
     proj = torch.randn(13, 100, generator=g).to(dt)
     outs = [torch.empty(13, n, device=DEV) for n in (24, 24, 40)]
@@ -423,7 +423,7 @@ def test_scaled_rotation_table_against_the_formula():
     """The table of the part against the plain one, for scalings that blend, that leave all pairs alone and that slow
     all of them down."""
     from llm_infer_engine_b200.parts.latent_attention import rotation_table
-    for dims, base, sc in ((8, 10000.0, (8.0, 64, 16.0, 2.0)), (32, 100000.0, (4.0, 128, 32.0, 1.0)),
+    for dims, base, sc in ((8, 10000.0, (8.0, 64, 16.0, 2.0)), (32, 100000.0, (3.0, 128, 16.0, 1.0)),
                            (4, 50.0, (2.0, 16, 4.0, 1.0)), (16, 10000.0, (40.0, 4096, 32.0, 1.0)), (8, 500.0, None)):
         rot = {"dims": dims, "base": base, "scaling": dict(zip(("factor", "original", "fast", "slow"), sc)) if sc else None}
         cos, sin = plain.rotary_table(300, rot)
