@@ -70,7 +70,7 @@ TINY_C = {"architecture": "Burinex", "vocab": 160, "width": 128, "postln_alpha":
      "mlp": _moe(4, 3, 32, 32)}]}
 CFGS = {"a": TINY_A, "b": TINY_B, "c": TINY_C}
 LENGTHS = {"a": [1, 5, 64, 65, 130, 300], "b": [3, 77, 200, 257], "c": [40, 129, 260]}
-SHARPEN = {"a": 1.4, "b": 1.5, "c": 2.0}        # factor on what makes the attention scores
+SHARPEN = {"a": 1.4, "b": 1.5, "c": 1.5}        # factor on what makes the attention scores
 _folders, _engines = {}, {}
 
 
