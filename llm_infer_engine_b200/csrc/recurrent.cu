@@ -68,7 +68,7 @@ constexpr int kScanRWide = 8;       // ... when it owns four columns
 // [n_seqs, NC, H, D]: MODE 1 runs a chunk that is not the sequence's last from a zero state, without outputs, and leaves
 // its end state in ws[c + 1] and the product of its gates in decay[c + 1]; MODE 2 runs a chunk from ws[c] with outputs,
 // and the last one writes the slot's state.
-template <typename T, int MODE, int C, int RMAX>
+template <typename T, int MODE, int C, int RMAX, bool KEYED>
 __global__ void __launch_bounds__(kScanThreads)
 matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, const T* __restrict__ v, int v_ld,
                    float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
@@ -77,7 +77,7 @@ matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, c
                    const float* __restrict__ head_decay) {
   pdl_launch_dependents();
   // keyed form: fg holds keys k_t instead of gates, and the gate of every row of head h is the constant head_decay[h]
-  const bool keyed = head_decay != nullptr;
+  constexpr bool keyed = KEYED;
   const float dh = keyed ? head_decay[blockIdx.y] : 0.f;       // a constant of the model: no kernel writes it
   pdl_wait();
   const int s = threadIdx.x & (S - 1);
@@ -176,7 +176,11 @@ matrix_scan_kernel(const float* __restrict__ qa, const float* __restrict__ fg, c
 struct ScanShape { int C, S, R; };
 static inline ScanShape scan_shape(int D, int Dv) {
   ScanShape g;
-  g.C = (Dv % 4 == 0 && D <= 32 * kScanRWide) ? 4 : 1;
+  // four columns a thread where the value size is a multiple of four and fills a block's threads that way (a narrow
+  // state would leave threads without columns); one column a thread otherwise
+  int s4 = 1;
+  while (s4 * kScanRWide < D) s4 <<= 1;
+  g.C = (Dv % 4 == 0 && s4 <= 32 && (kScanThreads / s4) * 4 <= Dv) ? 4 : 1;
   const int rmax = g.C == 4 ? kScanRWide : kScanR;
   g.S = 1;
   while (g.S * rmax < D) g.S <<= 1;
@@ -575,9 +579,14 @@ extern "C" int llmie_matrix_scan_ex(const float* qa, const float* fg, const void
   const int cols = (kScanThreads / S) * g.C;
   const dim3 grid((Dv + cols - 1) / cols, H, n_seqs), block(kScanThreads);
   if (grid.y > 65535 || grid.z > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
-#define LLMIE_SCAN0(T, C, RM)                                                                                            \
-  launch_k(matrix_scan_kernel<T, 0, C, RM>, grid, block, 0, stream, qa, fg, (const T*)v, v_ld, state, cu_q, seq_slot, o, \
+#define LLMIE_SCAN0_(T, C, RM, K)                                                                                           \
+  launch_k(matrix_scan_kernel<T, 0, C, RM, K>, grid, block, 0, stream, qa, fg, (const T*)v, v_ld, state, cu_q, seq_slot, o, \
            H, D, Dv, S, R, write_state, (float*)nullptr, (float*)nullptr, 0, 1, head_decay)
+#define LLMIE_SCAN0(T, C, RM)                                      \
+  do {                                                             \
+    if (head_decay) LLMIE_SCAN0_(T, C, RM, true);                  \
+    else LLMIE_SCAN0_(T, C, RM, false);                            \
+  } while (0)
   if (dtype == LLMIE_F32) {
     if (g.C == 4) LLMIE_SCAN0(float, 4, kScanRWide); else LLMIE_SCAN0(float, 1, kScanR);
   } else if (dtype == LLMIE_BF16) {
@@ -586,6 +595,7 @@ extern "C" int llmie_matrix_scan_ex(const float* qa, const float* fg, const void
     return LLMIE_ERR_DTYPE;
   }
 #undef LLMIE_SCAN0
+#undef LLMIE_SCAN0_
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -597,19 +607,19 @@ extern "C" int llmie_matrix_scan(const float* qa, const float* fg, const void* v
                               stream);
 }
 
-template <typename T, int C, int RM>
+template <typename T, int C, int RM, bool K>
 static void matrix_scan_chunked_launch(const float* qa, const float* fg, const T* v, int v_ld, float* state,
                                        const int* cu_q, const int* seq_slot, float* o, float* ws, float* decay,
                                        int n_seqs, int H, int D, int Dv, int S, int R, int L, int NC, int write_state,
                                        const float* head_decay, cudaStream_t stream) {
   const int cols = (kScanThreads / S) * C;
   const dim3 grid((Dv + cols - 1) / cols, H, n_seqs * NC), block(kScanThreads);
-  launch_k(matrix_scan_kernel<T, 1, C, RM>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
+  launch_k(matrix_scan_kernel<T, 1, C, RM, K>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
            write_state, ws, decay, L, NC, head_decay);
   const size_t HDDv = (size_t)H * D * Dv;
   launch_k(matrix_scan_chain_kernel, dim3((unsigned)((HDDv + 255) / 256), n_seqs), dim3(256), 0, stream,
            (const float*)state, cu_q, seq_slot, ws, (const float*)decay, H, D, Dv, L, NC);
-  launch_k(matrix_scan_kernel<T, 2, C, RM>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
+  launch_k(matrix_scan_kernel<T, 2, C, RM, K>, grid, block, 0, stream, qa, fg, v, v_ld, state, cu_q, seq_slot, o, H, D, Dv, S, R,
            write_state, ws, decay, L, NC, head_decay);
 }
 
@@ -626,9 +636,14 @@ extern "C" int llmie_matrix_scan_chunked_ex(const float* qa, const float* fg, co
   const ScanShape g = scan_shape(D, Dv);
   const int S = g.S, R = g.R;
   if (H > 65535 || (long long)n_seqs * n_chunks > 65535 || n_seqs > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
-#define LLMIE_SCANC(T, C, RM)                                                                                          \
-  matrix_scan_chunked_launch<T, C, RM>(qa, fg, (const T*)v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D, Dv, \
-                                       S, R, chunk, n_chunks, write_state, head_decay, stream)
+#define LLMIE_SCANC_(T, C, RM, K)                                                                                            \
+  matrix_scan_chunked_launch<T, C, RM, K>(qa, fg, (const T*)v, v_ld, state, cu_q, seq_slot, o, ws, decay, n_seqs, H, D, Dv, \
+                                          S, R, chunk, n_chunks, write_state, head_decay, stream)
+#define LLMIE_SCANC(T, C, RM)                                      \
+  do {                                                             \
+    if (head_decay) LLMIE_SCANC_(T, C, RM, true);                  \
+    else LLMIE_SCANC_(T, C, RM, false);                            \
+  } while (0)
   if (dtype == LLMIE_F32) {
     if (g.C == 4) LLMIE_SCANC(float, 4, kScanRWide); else LLMIE_SCANC(float, 1, kScanR);
   } else if (dtype == LLMIE_BF16) {
@@ -637,6 +652,7 @@ extern "C" int llmie_matrix_scan_chunked_ex(const float* qa, const float* fg, co
     return LLMIE_ERR_DTYPE;
   }
 #undef LLMIE_SCANC
+#undef LLMIE_SCANC_
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
